@@ -1,6 +1,6 @@
 """Prefill-shaped hot kernels, launched a few times each — target of `ncu --set full` (Qwen3-8B shapes, 4096 tokens).
 
-    ncu --set full --clock-control none --import-source on -k regex:'gemm_bf16_kernel|attn_prefill' -s 3 -c 3 \
+    ncu --set full --clock-control none -k regex:'gemm_bf16_kernel|attn_prefill' -s 3 -c 3 \
         -o gpurun_out/prefill python benchmarks/ncu_prefill_ops.py
 """
 import os

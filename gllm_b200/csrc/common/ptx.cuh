@@ -284,7 +284,7 @@ __device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wa
 __device__ __forceinline__ void griddep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // relaxed system-scope signals: issue ONE __threadfence_system() first, then any number of these (a
-// `*.release.sys` per peer costs one MEMBAR.ALL.SYS each — profiles/sass_summary.md)
+// `*.release.sys` per peer costs one system-wide fence each)
 __device__ __forceinline__ void red_add_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
