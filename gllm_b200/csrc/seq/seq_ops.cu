@@ -30,12 +30,14 @@ __global__ void embed_scale_kernel(const int* __restrict__ ids, const T* __restr
   for (int i = threadIdx.x; i < width; i += blockDim.x) out[(size_t)t * width + i] = to_f(row[i]) * scale;
 }
 
-// x += rms(y) * w_post ; x += add ; out = rms(x) * w_pre   (each part optional)
+// x += rms(y) * w_post * post_scale ; x += add ; out = rms(x) * w_pre   (each part optional; post_scale: an fp32
+// layer scale). With emit_plain and no w_pre, out = x rounded to T (sublayers that read the stream un-normed).
 template <typename T>
 __global__ void __launch_bounds__(256) resid_norm_kernel(float* __restrict__ x, const T* __restrict__ y, long ldy,
-                                                         const T* __restrict__ w_post, const float* __restrict__ add,
-                                                         const T* __restrict__ w_pre, T* __restrict__ out, int width,
-                                                         float eps) {
+                                                         const T* __restrict__ w_post,
+                                                         const float* __restrict__ post_scale,
+                                                         const float* __restrict__ add, const T* __restrict__ w_pre,
+                                                         T* __restrict__ out, int width, float eps, int emit_plain) {
   __shared__ float scratch[8];
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * width;
@@ -47,12 +49,18 @@ __global__ void __launch_bounds__(256) resid_norm_kernel(float* __restrict__ x, 
     ss = block_sum<256>(ss, scratch);
     r_post = 1.0f / sqrtf(ss / (float)width + eps);
   }
+  const bool plain = w_pre == nullptr && emit_plain && out != nullptr;
   float ss2 = 0.f;
   for (int i = threadIdx.x; i < width; i += 256) {
     float v = xr[i];
-    if (y != nullptr) v += to_f(y[(size_t)t * ldy + i]) * r_post * to_f(w_post[i]);
+    if (y != nullptr) {
+      float br = to_f(y[(size_t)t * ldy + i]) * r_post * to_f(w_post[i]);
+      if (post_scale != nullptr) br *= post_scale[i];
+      v += br;
+    }
     if (add != nullptr) v += add[(size_t)t * width + i];
     if (y != nullptr || add != nullptr) xr[i] = v;
+    if (plain) out[(size_t)t * width + i] = from_f<T>(v);
     ss2 += v * v;
   }
   if (w_pre == nullptr) return;
@@ -169,12 +177,15 @@ __global__ void __launch_bounds__(128) window_attn_kernel(
   }
 }
 
-// depthwise causal convolution + SiLU; taps before the chunk come from the sequence's carried state
+// depthwise causal convolution + SiLU (act 0) or no activation (act 1); taps before the chunk come from the
+// sequence's carried state. in_bias (optional) is added to every input at a position >= 0; the zeros before the
+// start of a sequence stay zeros, and the carried state holds the inputs without it.
 template <typename T>
 __global__ void conv_silu_kernel(const T* __restrict__ xz, long ldxz, int C, const float* __restrict__ w,
                                  const float* __restrict__ b, int taps, const T* __restrict__ state,
                                  const int* __restrict__ rec_slots, const int* __restrict__ seq_lens,
-                                 const int* __restrict__ qsl, int nseq, T* __restrict__ out) {
+                                 const int* __restrict__ qsl, int nseq, T* __restrict__ out, int act,
+                                 const float* __restrict__ in_bias) {
   const int t = blockIdx.x;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= C) return;
@@ -183,15 +194,18 @@ __global__ void conv_silu_kernel(const T* __restrict__ xz, long ldxz, int C, con
   const bool carried = state != nullptr && (seq_lens[s] - n) > 0;
   const T* st = carried ? state + (size_t)rec_slots[s] * (taps > 1 ? taps - 1 : 1) * C : nullptr;
   const int li = t - q0;
+  const int pos0 = seq_lens[s] - n;                 // position of the chunk's first token
+  const float ib = in_bias != nullptr ? in_bias[c] : 0.f;
   float acc = b[c];
   for (int j = 0; j < taps; ++j) {
     const int src = li - (taps - 1) + j;
     float v = 0.f;
     if (src >= 0) v = to_f(xz[(size_t)(q0 + src) * ldxz + c]);
     else if (carried) v = to_f(st[(size_t)(taps - 1 + src) * C + c]);
+    if (pos0 + src >= 0) v += ib;
     acc = fmaf(w[(size_t)c * taps + j], v, acc);
   }
-  out[(size_t)t * C + c] = from_f<T>(acc / (1.0f + expf(-acc)));
+  out[(size_t)t * C + c] = from_f<T>(act == 0 ? acc / (1.0f + expf(-acc)) : acc);
 }
 
 // after the convolution: state <- the last taps - 1 inputs of the sequence (shifting in what the chunk brought)
@@ -394,18 +408,19 @@ GLLM_EXPORT int gllm_seq_embed_scale(const void* ids, const void* table, void* o
   return 0;
 }
 
-GLLM_EXPORT int gllm_seq_resid_norm(void* x, const void* y, long ldy, const void* w_post, const void* add,
-                                    const void* w_pre, void* out, int ntok, int width, float eps, int is_f32,
-                                    void* stream) {
+GLLM_EXPORT int gllm_seq_resid_norm(void* x, const void* y, long ldy, const void* w_post, const void* post_scale,
+                                    const void* add, const void* w_pre, void* out, int ntok, int width, float eps,
+                                    int emit_plain, int is_f32, void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   GLLM_BY_DTYPE(is_f32,
                 (resid_norm_kernel<__nv_bfloat16><<<ntok, 256, 0, st>>>(
-                    (float*)x, (const __nv_bfloat16*)y, ldy, (const __nv_bfloat16*)w_post, (const float*)add,
-                    (const __nv_bfloat16*)w_pre, (__nv_bfloat16*)out, width, eps)),
+                    (float*)x, (const __nv_bfloat16*)y, ldy, (const __nv_bfloat16*)w_post, (const float*)post_scale,
+                    (const float*)add, (const __nv_bfloat16*)w_pre, (__nv_bfloat16*)out, width, eps, emit_plain)),
                 (resid_norm_kernel<float><<<ntok, 256, 0, st>>>((float*)x, (const float*)y, ldy, (const float*)w_post,
-                                                                (const float*)add, (const float*)w_pre, (float*)out,
-                                                                width, eps)));
+                                                                (const float*)post_scale, (const float*)add,
+                                                                (const float*)w_pre, (float*)out, width, eps,
+                                                                emit_plain)));
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }
@@ -451,14 +466,14 @@ GLLM_EXPORT int gllm_seq_window_attention(const void* q, const void* kc, const v
 
 GLLM_EXPORT int gllm_seq_conv_silu(const void* xz, long ldxz, int ntok, int nseq, int C, const void* w, const void* b,
                                    int taps, void* state, const void* rec_slots, const void* seq_lens, const void* qsl,
-                                   void* out, int is_f32, void* stream) {
+                                   void* out, int is_f32, int act, const void* in_bias, void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(ntok, (C + 127) / 128), sgrid(nseq, (C + 127) / 128);
   if (is_f32) {
     conv_silu_kernel<float><<<grid, 128, 0, st>>>((const float*)xz, ldxz, C, (const float*)w, (const float*)b, taps,
                                                   (const float*)state, (const int*)rec_slots, (const int*)seq_lens,
-                                                  (const int*)qsl, nseq, (float*)out);
+                                                  (const int*)qsl, nseq, (float*)out, act, (const float*)in_bias);
     if (state != nullptr && taps > 1)
       conv_state_update_kernel<float><<<sgrid, 128, 0, st>>>((const float*)xz, ldxz, C, taps, (float*)state,
                                                              (const int*)rec_slots, (const int*)seq_lens,
@@ -466,7 +481,8 @@ GLLM_EXPORT int gllm_seq_conv_silu(const void* xz, long ldxz, int ntok, int nseq
   } else {
     conv_silu_kernel<__nv_bfloat16><<<grid, 128, 0, st>>>(
         (const __nv_bfloat16*)xz, ldxz, C, (const float*)w, (const float*)b, taps, (const __nv_bfloat16*)state,
-        (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, nseq, (__nv_bfloat16*)out);
+        (const int*)rec_slots, (const int*)seq_lens, (const int*)qsl, nseq, (__nv_bfloat16*)out, act,
+        (const float*)in_bias);
     if (state != nullptr && taps > 1)
       conv_state_update_kernel<__nv_bfloat16><<<sgrid, 128, 0, st>>>(
           (const __nv_bfloat16*)xz, ldxz, C, taps, (__nv_bfloat16*)state, (const int*)rec_slots, (const int*)seq_lens,

@@ -99,18 +99,21 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_write_kernel(
 //     S <- g S;  u = delta ? beta (v - S^T k) : v;  S <- S + k u^T;  o = S^T q
 // costs two register passes and two PARTS-lane shuffle reductions (PARTS = 8 for head sizes >= 128: half the
 // registers per thread, twice the warps in flight). q / k rows and the per-token g, beta of TCH tokens are staged
-// in shared memory by the whole block (SiLU, unit length and the q scale applied there).
-template <typename T, int NS, int PARTS>
+// in shared memory by the whole block (SiLU, unit length and the q scale applied there). With KD the decay is one
+// value per key channel, g[d] = sigmoid(zk[d] + zk_bias[d])^inv_tau (a third staged row per token), acting on row d.
+template <typename T, int NS, int PARTS, bool KD>
 __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
     const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ v, long ldv,
     const T* __restrict__ beta, long ldb, const T* __restrict__ a, long lda, const float* __restrict__ neg_a,
     const float* __restrict__ dt_bias, const float* __restrict__ decay, float* __restrict__ state,
     const int* __restrict__ rec_slots, const int* __restrict__ seq_lens, const int* __restrict__ qsl, int H, int G,
-    int D, int V, int silu_in, int unit_qk, float q_scale, int delta, float* __restrict__ out) {
+    int D, int V, int silu_in, int unit_qk, float q_scale, int delta, float* __restrict__ out,
+    const T* __restrict__ zk, long ldz, const float* __restrict__ zk_bias, float inv_tau) {
   constexpr int TCH = 8;               // tokens staged per round (16 measured 2.4x slower: registers)
+  constexpr int ROWS = KD ? 3 : 2;
   extern __shared__ float sm[];
-  float* sq = sm;                      // [TCH][2][D]: q row, k row
-  float* sg = sm + TCH * 2 * D;        // [TCH][2]: g, beta
+  float* sq = sm;                      // [TCH][ROWS][D]: q row, k row (, decay row)
+  float* sg = sm + TCH * ROWS * D;     // [TCH][2]: g, beta
   const int s = blockIdx.x, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int NT = 32 * PARTS, NW = PARTS;       // threads and warps per block
@@ -132,16 +135,25 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
   for (int t0 = q0; t0 < q1; t0 += TCH) {
     const int nt = min(TCH, q1 - t0);
     __syncthreads();                             // the previous chunk's rows are consumed
-    for (int idx = threadIdx.x; idx < nt * 2 * D; idx += NT) {
-      const int kk = idx / (2 * D), r = idx - kk * 2 * D;
-      float f = r < D ? to_f(q[(size_t)(t0 + kk) * ldq + (size_t)kvh * D + r])
-                      : to_f(k[(size_t)(t0 + kk) * ldk + (size_t)kvh * D + r - D]);
-      if (silu_in) f = silu_f(f);
+    for (int idx = threadIdx.x; idx < nt * ROWS * D; idx += NT) {
+      const int kk = idx / (ROWS * D), r = idx - kk * ROWS * D;
+      float f;
+      if (KD && r >= 2 * D) {
+        const int c = h * D + r - 2 * D;
+        const float z = to_f(zk[(size_t)(t0 + kk) * ldz + c]) + (zk_bias != nullptr ? zk_bias[c] : 0.f);
+        f = expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * inv_tau);      // sigmoid(z)^inv_tau
+      } else {
+        f = r < D ? to_f(q[(size_t)(t0 + kk) * ldq + (size_t)kvh * D + r])
+                  : to_f(k[(size_t)(t0 + kk) * ldk + (size_t)kvh * D + r - D]);
+        if (silu_in) f = silu_f(f);
+      }
       sq[idx] = f;
     }
     if (threadIdx.x < nt) {
       float g, b = 1.0f;
-      if (decay != nullptr) {
+      if (KD) {
+        g = 1.0f;
+      } else if (decay != nullptr) {
         g = decay[h];
       } else {
         const float z = to_f(a[(size_t)(t0 + threadIdx.x) * lda + h]) + dt_bias[h];
@@ -154,7 +166,7 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
     __syncthreads();
     if (unit_qk || q_scale != 1.0f) {
       for (int row = warp; row < 2 * nt; row += NW) {      // row = token * 2 + (0: q, 1: k)
-        float* ptr = sq + (size_t)row * D;
+        float* ptr = sq + (size_t)((row >> 1) * ROWS + (row & 1)) * D;
         float sc = (row & 1) ? 1.0f : q_scale;
         if (unit_qk) {
           float ss = 0.f;
@@ -176,8 +188,9 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
 #pragma unroll
     for (int kk = 0; kk < TCH; ++kk) {
       if (kk < nt) {
-        const float* qq = sq + (size_t)kk * 2 * D;
+        const float* qq = sq + (size_t)kk * ROWS * D;
         const float* kr = qq + D;
+        const float* gr = qq + (ROWS - 1) * D;          // the decay row with KD
         const float g = sg[kk * 2], b = sg[kk * 2 + 1];
         float u = vv[kk];
         if (delta) {
@@ -196,7 +209,7 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
         for (int j = 0; j < NS; ++j) {
           const int d = part + PARTS * j;
           if (d < D) {
-            S[j] = fmaf(kr[d], u, g * S[j]);
+            S[j] = fmaf(kr[d], u, (KD ? gr[d] : g) * S[j]);
             o = fmaf(S[j], qq[d], o);
           }
         }
@@ -356,15 +369,19 @@ __global__ void __launch_bounds__(128) router_select_kernel(const float* __restr
     for (int kk = 0; kk < top_k; ++kk) wout[(size_t)t * top_k + kk] /= den;
 }
 
-// plain experts, first half: act[slot, f] = silu(gate_e[f] . h) * (up_e[f] . h); one warp per (slot, f)
+// plain experts, first half: act[slot, f] = silu(gate_e[f] . h) * (up_e[f] . h); one warp per (slot, f). With
+// limit > 0 the clamped form: g = min(gate, limit), u = clamp(up, +-limit), act = g sigmoid(alpha g) (u + 1).
+// An id >= n_real names an identity expert: nothing to compute here.
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* __restrict__ h, long ldh,
                                                           const T* __restrict__ w13, const int* __restrict__ ids,
-                                                          int top_k, int width, int F, T* __restrict__ act) {
+                                                          int top_k, int width, int F, T* __restrict__ act,
+                                                          int n_real, float limit, float alpha) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = blockIdx.x, f = blockIdx.y * 4 + warp;
   if (f >= F) return;
   const int e = ids[slot];
+  if (e >= n_real) return;
   const T* hr = h + (size_t)(slot / top_k) * ldh;
   const T* gr = w13 + ((size_t)e * 2 * F + f) * width;
   const T* ur = gr + (size_t)F * width;
@@ -376,20 +393,35 @@ __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* __restrict__ 
   }
   ga = warp_sum(ga);
   ua = warp_sum(ua);
-  if (lane == 0) act[(size_t)slot * F + f] = from_f<T>(silu_f(ga) * ua);
+  if (lane == 0) {
+    float r;
+    if (limit > 0.f) {
+      const float g = fminf(ga, limit), u = fminf(fmaxf(ua, -limit), limit);
+      r = g * sigmoid_f(alpha * g) * (u + 1.0f);
+    } else {
+      r = silu_f(ga) * ua;
+    }
+    act[(size_t)slot * F + f] = from_f<T>(r);
+  }
 }
 
-// plain experts, second half: out[t, c] = sum_k weight[t, k] * (down_e[c] . act[t * top_k + k]); one warp per (t, c)
+// plain experts, second half: out[t, c] = sum_k weight[t, k] * (down_e[c] . act[t * top_k + k]); one warp per (t, c).
+// An identity expert (id >= n_real) contributes weight * h[t, c].
 template <typename T>
 __global__ void __launch_bounds__(128) moe_down_kernel(const T* __restrict__ act, const T* __restrict__ w2,
                                                        const int* __restrict__ ids, const float* __restrict__ wts,
-                                                       int top_k, int width, int F, T* __restrict__ out) {
+                                                       int top_k, int width, int F, T* __restrict__ out,
+                                                       const T* __restrict__ h, long ldh, int n_real) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x, c = blockIdx.y * 4 + warp;
   if (c >= width) return;
   float total = 0.f;
   for (int kk = 0; kk < top_k; ++kk) {
     const int e = ids[(size_t)t * top_k + kk];
+    if (e >= n_real) {
+      total = fmaf(wts[(size_t)t * top_k + kk], to_f(h[(size_t)t * ldh + c]), total);
+      continue;
+    }
     const T* ar = act + ((size_t)t * top_k + kk) * F;
     const T* dr = w2 + ((size_t)e * width + c) * F;
     float acc = 0.f;
@@ -412,12 +444,17 @@ int state_dispatch(dim3 grid, size_t smem, cudaStream_t st, const void* q, long 
                    const void* v, long ldv, const void* beta, long ldb, const void* a, long lda, const float* neg_a,
                    const float* dt_bias, const float* decay, float* state, const int* rec_slots, const int* seq_lens,
                    const int* qsl, int H, int G, int D, int V, int silu_in, int unit_qk, float q_scale, int delta,
-                   float* out, int parts) {
-#define GLLM_STATE(NS, PARTS)                                                                                       \
-  linear_state_kernel<T, NS, PARTS><<<grid, 32 * PARTS, smem, st>>>((const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, \
-                                                      (const T*)beta, ldb, (const T*)a, lda, neg_a, dt_bias, decay, \
-                                                      state, rec_slots, seq_lens, qsl, H, G, D, V, silu_in, unit_qk, \
-                                                      q_scale, delta, out)
+                   float* out, int parts, const void* zk, long ldz, const float* zk_bias, float inv_tau) {
+#define GLLM_STATE_KD(NS, PARTS, KD)                                                                                \
+  linear_state_kernel<T, NS, PARTS, KD><<<grid, 32 * PARTS, smem, st>>>(                                            \
+      (const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, (const T*)beta, ldb, (const T*)a, lda, neg_a, dt_bias,  \
+      decay, state, rec_slots, seq_lens, qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta, out, (const T*)zk, ldz, \
+      zk_bias, inv_tau)
+#define GLLM_STATE(NS, PARTS)                                               \
+  do {                                                                      \
+    if (zk != nullptr) GLLM_STATE_KD(NS, PARTS, true);                      \
+    else GLLM_STATE_KD(NS, PARTS, false);                                   \
+  } while (0)
   if (D <= 16) GLLM_STATE(4, 4);
   else if (D <= 32) GLLM_STATE(8, 4);
   else if (D <= 64) GLLM_STATE(16, 4);
@@ -425,6 +462,7 @@ int state_dispatch(dim3 grid, size_t smem, cudaStream_t st, const void* q, long 
   else if (D <= 256) { if (parts == 8) GLLM_STATE(32, 8); else GLLM_STATE(64, 4); }
   else return 2;
 #undef GLLM_STATE
+#undef GLLM_STATE_KD
   return 0;
 }
 
@@ -474,22 +512,25 @@ GLLM_EXPORT int gllm_seq_linear_state(const void* q, long ldq, const void* k, lo
                                       const void* dt_bias, const void* decay, void* state, const void* rec_slots,
                                       const void* seq_lens, const void* qsl, int nseq, int H, int G, int D, int V,
                                       int silu_in, int unit_qk, float q_scale, int delta, void* out, int is_f32,
-                                      int parts, void* stream) {
+                                      int parts, const void* zk, long ldz, const void* zk_bias, float inv_tau,
+                                      void* stream) {
   if (nseq <= 0) return 0;
+  if (zk != nullptr && (delta || G != H)) return 2;                    // key-channel decay: plain update, own keys
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(nseq, H, (V + 31) / 32);
-  const size_t smem = (size_t)(8 * 2 * D + 16) * sizeof(float);      // TCH rows of q and k + TCH (g, beta)
+  // TCH rows of q and k (and the decay row) + TCH (g, beta)
+  const size_t smem = (size_t)(8 * (zk != nullptr ? 3 : 2) * D + 16) * sizeof(float);
   int rc;
   if (is_f32)
     rc = state_dispatch<float>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
                                (const float*)dt_bias, (const float*)decay, (float*)state, (const int*)rec_slots,
                                (const int*)seq_lens, (const int*)qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta,
-                               (float*)out, parts);
+                               (float*)out, parts, zk, ldz, (const float*)zk_bias, inv_tau);
   else
     rc = state_dispatch<bf16_t>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
                                 (const float*)dt_bias, (const float*)decay, (float*)state, (const int*)rec_slots,
                                 (const int*)seq_lens, (const int*)qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta,
-                                (float*)out, parts);
+                                (float*)out, parts, zk, ldz, (const float*)zk_bias, inv_tau);
   if (rc) return rc;
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
@@ -564,20 +605,22 @@ GLLM_EXPORT int gllm_seq_router_select(const void* logits, int ntok, int E, int 
 
 GLLM_EXPORT int gllm_seq_routed_experts(const void* h, long ldh, const void* w13, const void* w2, const void* ids,
                                         const void* wts, int ntok, int top_k, int width, int F, void* act, void* out,
-                                        int is_f32, void* stream) {
+                                        int is_f32, int n_real, float limit, float alpha, void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 g1(ntok * top_k, (F + 3) / 4), g2(ntok, (width + 3) / 4);
   if (is_f32) {
     moe_gate_up_kernel<float><<<g1, 128, 0, st>>>((const float*)h, ldh, (const float*)w13, (const int*)ids, top_k,
-                                                  width, F, (float*)act);
+                                                  width, F, (float*)act, n_real, limit, alpha);
     moe_down_kernel<float><<<g2, 128, 0, st>>>((const float*)act, (const float*)w2, (const int*)ids,
-                                               (const float*)wts, top_k, width, F, (float*)out);
+                                               (const float*)wts, top_k, width, F, (float*)out, (const float*)h, ldh,
+                                               n_real);
   } else {
     moe_gate_up_kernel<bf16_t><<<g1, 128, 0, st>>>((const bf16_t*)h, ldh, (const bf16_t*)w13, (const int*)ids, top_k,
-                                                   width, F, (bf16_t*)act);
+                                                   width, F, (bf16_t*)act, n_real, limit, alpha);
     moe_down_kernel<bf16_t><<<g2, 128, 0, st>>>((const bf16_t*)act, (const bf16_t*)w2, (const int*)ids,
-                                                (const float*)wts, top_k, width, F, (bf16_t*)out);
+                                                (const float*)wts, top_k, width, F, (bf16_t*)out, (const bf16_t*)h, ldh,
+                                                n_real);
   }
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;

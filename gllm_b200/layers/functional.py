@@ -125,10 +125,10 @@ def embedding_scaled(ids, table, scale):
     return ref.embedding_scaled(ids, table, scale)
 
 
-def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype):
+def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None):
     if x.is_cuda:
-        return _seq().resid_norm(x, y, w_post, add, w_pre, eps, out_dtype)
-    return ref.resid_norm(x, y, w_post, add, w_pre, eps, out_dtype)
+        return _seq().resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale)
+    return ref.resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale)
 
 
 def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, k_cache, v_cache, slots):
@@ -148,11 +148,12 @@ def window_attention(q, k_cache, v_cache, inp, scale, num_q_heads, head_dim, win
                                 num_q_heads, head_dim, window, sink)
 
 
-def causal_conv_silu(xz, channels, w, b, conv_state, inp):
+def causal_conv_silu(xz, channels, w, b, conv_state, inp, act="silu", in_bias=None):
+    """Depthwise causal convolution with carried taps; `act` "silu" | "none"; `in_bias` is added to every input
+    that exists (not to the zeros before a sequence's start)."""
     slots = inp.rec_slots if conv_state is not None else None
-    if xz.is_cuda:
-        return _seq().causal_conv_silu(xz, channels, w, b, conv_state, slots, inp.seq_lens, inp.query_start_loc)
-    return ref.causal_conv_silu(xz, channels, w, b, conv_state, slots, inp.seq_lens, inp.query_start_loc)
+    fn = _seq().causal_conv_silu if xz.is_cuda else ref.causal_conv_silu
+    return fn(xz, channels, w, b, conv_state, slots, inp.seq_lens, inp.query_start_loc, act, in_bias)
 
 
 def selective_scan(xc, dt_raw, proj, xz, a, d_skip, dt_bias, ssm_state, inp, channels, nstate, dt_rank):
@@ -197,11 +198,11 @@ def masked_attention(q, k_cache, v_cache, inp, scale, num_q_heads, head_dim, v_d
 
 
 def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, inp, heads, qk_heads, dim, v_dim, silu_in,
-                      unit_qk, q_scale, delta):
+                      unit_qk, q_scale, delta, zk=None, zk_bias=None, inv_tau=1.0):
     slots = inp.rec_slots if state is not None else None
     fn = _seq().linear_state_scan if q.is_cuda else ref.linear_state_scan
     return fn(q, k, v, beta, a, neg_a, dt_bias, decay, state, slots, inp.seq_lens, inp.query_start_loc, heads,
-              qk_heads, dim, v_dim, silu_in, unit_qk, q_scale, delta)
+              qk_heads, dim, v_dim, silu_in, unit_qk, q_scale, delta, zk, zk_bias, inv_tau)
 
 
 def gated_group_norm(o, gate, w, group, eps, act, out_scale=1.0, out=None, out_dtype=None):
@@ -238,3 +239,67 @@ def softcap(z, cap):
     if z.is_cuda:
         return _seq().softcap(z, cap)
     return ref.softcap(z, cap)
+
+
+# -- branch-norm blocks, key-decay linear attention, latent attention, gated linear recurrent unit, grouped routing
+# with identity experts and clamped gated experts (csrc/seq/latent_ops.cu) ------------------------------------
+def _lat():
+    from gllm_b200.ops import sm100_latent
+    return sm100_latent
+
+
+def rms_rows(x, w, eps):
+    return _lat().rms_rows(x, w, eps) if x.is_cuda else ref.rms_rows(x, w, eps)
+
+
+def block_linear(x, w, out_dtype=None):
+    """Block-diagonal linear map x [T, B * K] x w [B, N, K] -> [T, B * N]."""
+    return _lat().block_linear(x, w, out_dtype) if x.is_cuda else ref.block_linear(x, w, out_dtype)
+
+
+def linear_batched(a, w, out):
+    """out[:, b, :] = a[:, b, :] @ w[b].T (strided views allowed): the tcgen05 GEMM's batched mode for aligned
+    bf16 operands, the plain batched kernel otherwise (true fp32 for fp32 operands)."""
+    return _lat().linear_batched(a, w, out) if a.is_cuda else ref.linear_batched(a, w, out)
+
+
+def rglru_scan(u, gates, gate_bias, c_decay, y_pre, y_bias, state, inp, block, out_dtype):
+    slots = inp.rec_slots if state is not None else None
+    fn = _lat().rglru_scan if u.is_cuda else ref.rglru_scan
+    return fn(u, gates, gate_bias, c_decay, y_pre, y_bias, state, slots, inp.seq_lens, inp.query_start_loc, block,
+              out_dtype)
+
+
+def latent_norm_rope_write(q, dkv, rank, rot, norm_w, eps, positions, freqs, mag, q_full, cache, slots):
+    fn = _lat().latent_norm_rope_write if q.is_cuda else ref.latent_norm_rope_write
+    return fn(q, dkv, rank, rot, norm_w, eps, positions, freqs, mag, q_full, cache, slots)
+
+
+def latent_attention(q_full, cache, inp, scale, rank):
+    """Causal multi-query attention over the paged latent cache (values = the first `rank` columns of the keys)."""
+    if q_full.is_cuda:
+        return _lat().latent_attention(q_full, cache, inp, scale, rank)
+    return ref.latent_attention(q_full, cache, inp.block_table, inp.seq_lens, inp.query_start_loc, scale, rank)
+
+
+def grouped_router(h, w, correction, top_k, n_groups, keep_groups, scale):
+    fn = _lat().grouped_router if h.is_cuda else ref.grouped_router
+    return fn(h, w, correction, top_k, n_groups, keep_groups, scale)
+
+
+def glu_clamp(gu, limit, alpha=1.702):
+    return _lat().glu_clamp(gu, limit, alpha) if gu.is_cuda else ref.glu_clamp(gu, limit, alpha)
+
+
+def linear_glu_clamp(x, w_interleaved, limit, alpha=1.702):
+    """glu_clamp(x @ w^T) as the tcgen05 GEMM's gated epilogue (gate / up rows interleaved per 128)."""
+    if x.is_cuda:
+        return _lat().linear_glu_clamp(x, w_interleaved, limit, alpha)
+    return ref.linear_glu_clamp(x, w_interleaved, limit, alpha)
+
+
+def routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha=1.702):
+    """Clamped gated experts; ids >= the number of experts are identity experts."""
+    if h.is_cuda:
+        return _lat().routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha)
+    return ref.routed_glu_experts(h, w13, w2, weights, ids, limit, alpha)

@@ -9,6 +9,10 @@ in a state slot of the engine's cache:
   * `DecayLinearCore` — linear attention with a constant decay per head: q, k, v = SiLU(projection),
         S <- decay S + k v^T;  o = S^T q
     then one RMS norm over all heads together, times sigmoid(gate).
+  * `KeyDecayLinearCore` — gated linear attention with one decay per key channel, from a low-rank projection:
+        z = W2 (W1 h) + b;  a = sigmoid(z)^(1 / tau)  [heads, dim];  S <- diag(a) S + k v^T;  o = S^T q
+    (q times dim^-1/2 by default), then per-head RMS norm over v_dim with one weight shared by the heads, times
+    SiLU(gate).
 
 A core maps its slice of a joint input projection to its slice of a joint pre-output buffer, so that several cores
 can share one input GEMM and one output GEMM (`layers/parallel_mixer.py`).
@@ -94,4 +98,40 @@ class DecayLinearCore(nn.Module):
                                    out_scale, out, proj.dtype)
 
     def load_extra(self, reader, pre, put):
+        put(self.norm_w, reader.get(pre + "norm"))
+
+
+class KeyDecayLinearCore(nn.Module):
+    uses_pages, uses_state = False, True
+    in_names = ("q", "k", "v", "g", "a1")
+
+    def __init__(self, heads: int, dim: int, v_dim: int, low_rank: int, tau: float, eps: float, dtype, device,
+                 q_scale=None):
+        super().__init__()
+        self.heads, self.dim, self.v_dim, self.low_rank, self.eps = heads, dim, v_dim, low_rank, eps
+        self.inv_tau = 1.0 / float(tau)
+        self.q_scale = float(dim) ** -0.5 if q_scale is None else float(q_scale)
+        self.n_qk, self.n_v = heads * dim, heads * v_dim
+        self.in_rows = (self.n_qk, self.n_qk, self.n_v, self.n_v, low_rank)
+        self.n_in, self.n_out = sum(self.in_rows), self.n_v
+        self.a2_w = _par(self.n_qk, low_rank, dtype=dtype, device=device)
+        self.a2_b = _par(self.n_qk, dtype=torch.float32, device=device)
+        self.norm_w = _par(v_dim, dtype=dtype, device=device)
+
+    def cache_entry(self):
+        return {"kind": "linear", "heads": self.heads, "dim": self.dim, "vdim": self.v_dim, "taps": 1, "channels": 0}
+
+    def core(self, inp, proj, cache, run_id, out, out_scale=1.0):
+        state = cache.ssm_state[run_id] if cache is not None else None
+        nq, nv = self.n_qk, self.n_v
+        z = Fn.linear_any(proj[:, 2 * nq + 2 * nv:2 * nq + 2 * nv + self.low_rank], self.a2_w)
+        o = Fn.linear_state_scan(proj[:, :nq], proj[:, nq:2 * nq], proj[:, 2 * nq:2 * nq + nv], None, None, None, None,
+                                 None, state, inp, self.heads, self.heads, self.dim, self.v_dim, False, False,
+                                 self.q_scale, False, zk=z, zk_bias=self.a2_b, inv_tau=self.inv_tau)
+        return Fn.gated_group_norm(o, proj[:, 2 * nq + nv:2 * nq + 2 * nv], self.norm_w, self.v_dim, self.eps, "silu",
+                                   out_scale, out, proj.dtype)
+
+    def load_extra(self, reader, pre, put):
+        put(self.a2_w, reader.get(pre + "a2"))
+        put(self.a2_b, reader.get(pre + "a2.b").float())
         put(self.norm_w, reader.get(pre + "norm"))

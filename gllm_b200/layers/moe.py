@@ -268,3 +268,71 @@ class SelectedSoftmaxMoE(nn.Module):
             gu = ref.interleave_gate_up(gu, 64)
         self.w13.data[e].copy_(gu)
         self.w2.data[e].copy_(down)
+
+
+class ClampedGLUMLP(nn.Module):
+    """down(g sigmoid(alpha g) (u + 1)) with g = min(gate h, limit), u = clamp(up h, -limit, limit); gate and up
+    rows share one GEMM. On CUDA in bf16 with ff % 128 == 0 the rows are stored interleaved per 128 and the
+    activation is the tcgen05 GEMM's gated epilogue."""
+
+    def __init__(self, hidden: int, ff: int, limit: float, dtype, device, alpha: float = 1.702):
+        super().__init__()
+        self.ff, self.limit, self.alpha = ff, float(limit), float(alpha)
+        self.fused = torch.device(device).type == "cuda" and dtype == torch.bfloat16 and ff % 128 == 0 and \
+            hidden % 8 == 0
+        self.gate_up_w = _param(2 * ff, hidden, dtype=dtype, device=device)
+        self.down_w = _param(hidden, ff, dtype=dtype, device=device)
+
+    def load(self, gate, up, down):
+        gu = torch.cat([gate, up], 0)
+        self.gate_up_w.data.copy_(ref.interleave_gate_up(gu, 128) if self.fused else gu)
+        self.down_w.data.copy_(down)
+
+    def forward(self, h):
+        if self.fused:
+            return Fn.linear_any(Fn.linear_glu_clamp(h, self.gate_up_w, self.limit, self.alpha), self.down_w)
+        return Fn.linear_any(Fn.glu_clamp(Fn.linear_any(h, self.gate_up_w), self.limit, self.alpha), self.down_w)
+
+
+class GroupedGLUMoE(nn.Module):
+    """Routed feed-forward with a softmax over ALL router outputs, a correction added to the scores for the choice
+    only, group-limited choice (a group's score is its best corrected score), identity experts (the last
+    `identity` router outputs: the result is the token itself times the weight, no tensors), weights renormalised
+    over the chosen and scaled, clamped gated experts (`ClampedGLUMLP` form) and an optional shared expert of the
+    same form that every token passes. One GPU. On CUDA in bf16 with ff % 64 == 0 and hidden % 128 == 0 the
+    experts run as the grouped tcgen05 GEMM pair (per-64 interleaved gate / up rows), otherwise on the plain
+    per-slot kernels (true fp32 for fp32 weights)."""
+
+    def __init__(self, num_experts: int, identity: int, top_k: int, hidden: int, ff: int, limit: float, n_groups: int,
+                 keep_groups: int, scale: float, dtype, device, shared_ff: int = 0, shared_limit: float = 0.0,
+                 alpha: float = 1.702):
+        super().__init__()
+        n_out = num_experts + identity
+        assert 1 <= top_k <= n_out and n_groups >= 1 and n_out % n_groups == 0 and 1 <= keep_groups <= n_groups
+        assert top_k <= keep_groups * (n_out // n_groups), "fewer eligible experts than choices"
+        self.num_experts, self.identity, self.top_k, self.hidden, self.ff = num_experts, identity, top_k, hidden, ff
+        self.limit, self.alpha, self.n_groups, self.keep_groups, self.scale = \
+            float(limit), float(alpha), n_groups, keep_groups, float(scale)
+        self.router_w = _param(n_out, hidden, dtype=dtype, device=device)
+        self.correction = nn.Parameter(torch.zeros(n_out, dtype=torch.float32, device=device), requires_grad=False)
+        self.w13 = _param(max(num_experts, 1), 2 * ff, hidden, dtype=dtype, device=device)
+        self.w2 = _param(max(num_experts, 1), hidden, ff, dtype=dtype, device=device)
+        self.interleaved = torch.device(device).type == "cuda" and dtype == torch.bfloat16 and ff % 64 == 0 and \
+            hidden % 128 == 0 and num_experts > 0
+        self.shared = ClampedGLUMLP(hidden, shared_ff, shared_limit, dtype, device, alpha) if shared_ff > 0 else None
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        w, ids = Fn.grouped_router(h, self.router_w, self.correction, self.top_k, self.n_groups, self.keep_groups,
+                                   self.scale)
+        out = Fn.routed_glu_experts(h, self.w13[: self.num_experts], self.w2[: self.num_experts], w, ids, self.limit,
+                                    self.interleaved, self.alpha)
+        if self.shared is not None:
+            out = out + self.shared(h)
+        return out
+
+    def load_expert(self, e: int, gate: torch.Tensor, up: torch.Tensor, down: torch.Tensor):
+        gu = torch.cat([gate, up], dim=0)
+        if self.interleaved:
+            gu = ref.interleave_gate_up(gu, 64)
+        self.w13.data[e].copy_(gu)
+        self.w2.data[e].copy_(down)

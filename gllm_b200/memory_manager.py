@@ -55,6 +55,9 @@ class HybridCache:
                                                      -> ssm_state[r] [slots, heads, dim, vdim] fp32 (one matrix per
                                                         head) and, with taps > 1, conv_state[r] [slots, taps - 1,
                                                         channels]
+      {"kind": "latent", "dim"}                      -> k_cache[r] only: one shared row of width dim per token (latent
+                                                        attention: [latent | rotated key part]), paged like one KV
+                                                        head; v_cache[r] is None (the values are columns of the row)
       {"kind": "multi", "kv": entry | None, "rec": entry | None}   -> a run that keeps both pages and state
     Slot contents are never cleared on re-use: the kernels start from zeros for a chunk at position 0."""
 
@@ -63,7 +66,7 @@ class HybridCache:
         """-> (paged entry | None, recurrent entry | None)"""
         if e["kind"] == "multi":
             return e.get("kv"), e.get("rec")
-        if e["kind"] == "kv":
+        if e["kind"] in ("kv", "latent"):
             return e, None
         if e["kind"] in ("ssm", "linear"):
             return None, e
@@ -84,7 +87,9 @@ class HybridCache:
         for e in layout:
             k = v = cs = ss = None
             kv, rec = self._parts(e)
-            if kv is not None:
+            if kv is not None and kv["kind"] == "latent":
+                k = torch.zeros(kv_cache_shape(num_pages, 1, kv["dim"], page_size), dtype=dtype, device=device)
+            elif kv is not None:
                 k = torch.zeros(kv_cache_shape(num_pages, kv["heads"], kv["dim"], page_size), dtype=dtype,
                                 device=device)
                 v = torch.zeros(kv_cache_shape(num_pages, kv["heads"], kv.get("vdim", kv["dim"]), page_size),
@@ -101,7 +106,8 @@ class HybridCache:
     @staticmethod
     def bytes_per_page(layout, page_size: int, dtype_bytes: int) -> int:
         kvs = [HybridCache._parts(e)[0] for e in layout]
-        return sum(page_size * e["heads"] * (e["dim"] + e.get("vdim", e["dim"])) * dtype_bytes
+        return sum(page_size * (e["dim"] if e["kind"] == "latent" else
+                                e["heads"] * (e["dim"] + e.get("vdim", e["dim"]))) * dtype_bytes
                    for e in kvs if e is not None)
 
     @staticmethod

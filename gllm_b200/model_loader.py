@@ -74,12 +74,14 @@ class ModelLoader:
         return list(eos) if isinstance(eos, (list, tuple)) else [eos]
 
     def load_model(self, device, progress=None):
+        dummy = self.load_format == "dummy" or isinstance(self.model_path, dict) or \
+            (isinstance(self.model_path, str) and self.model_path.startswith("preset:"))
+        reader = None if dummy else CheckpointReader(self.model_path)
+        registry.complete_config(self.config, reader)
         model = registry.build_model(self.config, device)
-        if self.load_format == "dummy" or isinstance(self.model_path, dict) or \
-                (isinstance(self.model_path, str) and self.model_path.startswith("preset:")):
+        if dummy:
             model.init_dummy()
         else:
-            reader = CheckpointReader(self.model_path)
             model.load_weights(reader, progress)
         if hasattr(model, "process_weights"):
             model.process_weights()

@@ -109,7 +109,7 @@ class ModelRunner:
         mrope = self.model.rope.mrope_section is not None if hasattr(self.model, "rope") else False
         self.input_data = InputData(self.max_num_batched_tokens, max(self.max_running_seqs, 1), max_blocks,
                                     self.device, mrope=mrope)
-        self.input_data.need_tok_seq = bool(self.loader.use_mla)
+        self.input_data.need_tok_seq = bool(self.loader.use_mla) or bool(getattr(self.model, "needs_tok_seq", False))
         # vocab-parallel sampling: the forward (and its CUDA graphs) ends at this rank's logits shard
         # test hook (tests/mp_tp_check.py): keep the full last-token logits of every step, per emitting sequence id
         self.keep_logits = os.environ.get("GLLM_KEEP_LOGITS", "0") == "1"

@@ -3,7 +3,15 @@ residual stream. Two block forms: sandwich norms around each sublayer with an op
 layers with shared weights (architecture `Saritar`: windowed sink attention and Mamba-1 mixers, squared-ReLU
 feed-forward), and norm-after-sum blocks (architecture `Femolix`: gated delta rule mixers and parallel mixers of
 chunk-masked rotary attention beside constant-decay linear attention, gated SiLU feed-forward, dense or routed, capped
-logits):
+logits), and branch-norm blocks with a layer scale (architecture `Bevovik`: real-gated linear recurrent units,
+key-decay gated linear attention and latent attention with YaRN rotary, a grouped mixture of clamped gated experts
+with identity experts and a shared expert):
+
+    x = embed[token]
+    per layer:  x += ls1 * rms(mixer(x)) * n1 ;  x += ls2 * rms(ff(x)) * n2            (sublayers read x itself)
+    logits = head @ (rms(x) * final_norm)
+
+The norm-after-sum form:
 
     x = embed[token]
     per layer:  x <- rms(alpha x + mixer(x)) * n1 ;  x <- rms(alpha x + ff(x)) * n2     (second line only with a ff)
@@ -24,10 +32,14 @@ optionally adds the embedding (loop re-entry) and emits the next sublayer's pre-
 In the norm-after-sum form one kernel per sublayer (`Fn.postnorm`) scales the stream, adds the sublayer's output,
 norms, writes the stream back and emits it in the compute dtype for the next sublayer.
 
+In the branch-norm form one kernel per sublayer (`Fn.resid_norm` with a layer scale) norms the branch, adds it into
+the stream and emits the stream in the compute dtype for the next sublayer (the stream itself in fp32).
+
 config.json keys read here: architecture, vocab, width, embedding.scale, norm.eps, loop.{start,stop,times},
-postln_alpha, logit_softcap, layers[i].{type, mixer{...}, mlp{kind, ff | expert.ff, router.{experts, top}} | null},
-optional torch_dtype. Tensor names: embed, head, final.norm, l<i>.norm1|norm1b|norm2|norm2b, l<i>.mix.*,
-l<i>.mlp.up|down|gate|router|e<j>.{gate,up,down}.
+postln_alpha, logit_softcap, layers[i].{type, mixer{...}, mlp{kind, ff | expert.{ff, limit}, router.{experts, top,
+identity, scale, groups.{count, keep}}, shared.{ff, limit}} | null}, optional torch_dtype. Tensor names: embed, head,
+final.norm, l<i>.norm1|norm1b|norm2|norm2b|ls1|ls2, l<i>.mix.*, l<i>.mlp.up|down|gate|router|correction|
+e<j>.{gate,up,down}|shared.{gate,up,down}.
 """
 from __future__ import annotations
 
@@ -38,10 +50,11 @@ import torch
 from torch import nn
 
 from gllm_b200.layers import functional as Fn
-from gllm_b200.layers.linear_attention import DecayLinearCore, GatedDeltaCore
-from gllm_b200.layers.moe import SelectedSoftmaxMoE
+from gllm_b200.layers.latent_attention import LatentAttention
+from gllm_b200.layers.linear_attention import DecayLinearCore, GatedDeltaCore, KeyDecayLinearCore
+from gllm_b200.layers.moe import GroupedGLUMoE, SelectedSoftmaxMoE
 from gllm_b200.layers.parallel_mixer import CoreMixer
-from gllm_b200.layers.ssm import Mamba1Mixer
+from gllm_b200.layers.ssm import Mamba1Mixer, RGLRUMixer
 from gllm_b200.layers.window_attention import RotaryChunkCore, SinkWindowAttention
 from gllm_b200.parallel import state as ps
 
@@ -61,10 +74,13 @@ class HybridSpec:
     loop_stop: int = 0
     loop_times: int = 1
     dtype: torch.dtype = torch.bfloat16
-    block: str = "sandwich"            # "sandwich": x += post(f(pre(x))) | "postnorm": x <- norm(alpha x + f(x))
+    # "sandwich": x += post(f(pre(x))) | "postnorm": x <- norm(alpha x + f(x)) | "branchnorm": x += ls * post(f(x))
+    block: str = "sandwich"
     resid_alpha: float = 1.0
     logit_softcap: float = 0.0         # 0: none
-    ff_act: str = "relu2"              # "relu2": down(relu(up h)^2) | "silu_gate": down(silu(gate h) * up h)
+    # "relu2": down(relu(up h)^2) | "silu_gate": down(silu(gate h) * up h) | "glu_clamp": clamped gate and up,
+    # down(g sigmoid(1.702 g) (u + 1))
+    ff_act: str = "relu2"
     eos_token_id: Optional[object] = None
     use_mla: bool = False
     quant: Optional[str] = None
@@ -96,6 +112,15 @@ def spec_femolix(cfg) -> HybridSpec:
                       dtype=_DTYPES[dt], block="postnorm", resid_alpha=float(cfg.get("postln_alpha", 1.0)),
                       logit_softcap=float(cfg.get("logit_softcap") or 0.0), ff_act="silu_gate",
                       eos_token_id=cfg.get("eos_token_id"))
+
+
+def spec_bevovik(cfg) -> HybridSpec:
+    dt = cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))
+    if dt not in _DTYPES:
+        raise ValueError(f"unsupported dtype {dt} for this architecture (bfloat16 | float32)")
+    return HybridSpec(arch="bevovik", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
+                      rms_eps=float(cfg["norm"]["eps"]), embed_scale=1.0, layers=[dict(x) for x in cfg["layers"]],
+                      dtype=_DTYPES[dt], block="branchnorm", ff_act="glu_clamp", eos_token_id=cfg.get("eos_token_id"))
 
 
 def layer_runs(n_layers: int, start: int, stop: int, times: int):
@@ -144,6 +169,20 @@ def make_mixer(kind: str, m: dict, spec: HybridSpec, device):
                                 spec.rms_eps, dt, device)
         return CoreMixer(h, [left, right], ["left", "right"], [float(m.get("left_scale", 1.0)),
                                                                float(m.get("right_scale", 1.0))], dt, device)
+    if kind == "gla":
+        a1 = m.get("low_rank")
+        core = KeyDecayLinearCore(int(m["heads"]), int(m["dim"]), int(m.get("vdim", m["dim"])),
+                                  int(a1) if a1 is not None else 16, float(m["tau"]), spec.rms_eps, dt, device)
+        return CoreMixer(h, [core], [""], [1.0], dt, device)
+    if kind == "rglru":
+        return RGLRUMixer(h, int(m["width"]), int(m["blocks"]), int(m["conv"]), dt, device)
+    if kind == "latent_attention":
+        rot = m.get("rot") or {}
+        rd = int(m.get("rot_dim", rot.get("dims", 0)))
+        assert int(rot.get("dims", rd)) == rd, "the rotated part is rotated whole"
+        return LatentAttention(h, int(m["heads"]), int(m["dim"]), rd, int(m.get("vdim", m["dim"])), int(m["q_rank"]),
+                               int(m["kv_rank"]), float(m["scale"]), float(rot.get("base", 10000.0)),
+                               rot.get("scaling"), spec.rms_eps, dt, device)
     raise ValueError(f"unknown mixer type {kind!r}")
 
 
@@ -179,6 +218,13 @@ def make_ff(mlp: dict, spec: HybridSpec, device):
     if kind == "moe" and spec.ff_act == "silu_gate":
         return SelectedSoftmaxMoE(int(mlp["router"]["experts"]), int(mlp["router"]["top"]), h,
                                   int(mlp["expert"]["ff"]), dt, device)
+    if kind == "moe" and spec.ff_act == "glu_clamp":
+        r, e, sh = mlp["router"], mlp["expert"], mlp.get("shared") or {}
+        groups = r.get("groups") or {}
+        return GroupedGLUMoE(int(r["experts"]), int(r.get("identity", 0)), int(r["top"]), h, int(e["ff"]),
+                             float(e["limit"]), int(groups.get("count", 1)), int(groups.get("keep", 1)),
+                             float(r.get("scale", 1.0)), dt, device, shared_ff=int(sh.get("ff", 0)),
+                             shared_limit=float(sh.get("limit", 0.0)))
     raise ValueError(f"unknown feed-forward kind {kind!r}")
 
 
@@ -194,11 +240,18 @@ class HybridLayer(nn.Module):
         self.layer_id = layer_id
         self.kind = L["type"]
         sandwich = spec.block == "sandwich"
+        scaled = spec.block == "branchnorm"          # a layer scale per sublayer, fp32
+
+        def scale():
+            return nn.Parameter(torch.ones(h, dtype=torch.float32, device=device), requires_grad=False)
+
         self.norm1_w, self.norm1b_w = norm(), (norm() if sandwich else None)
+        self.ls1 = scale() if scaled else None
         self.mixer = make_mixer(L["type"], L["mixer"], spec, device)
         mlp = L.get("mlp")
         if mlp is not None:
             self.norm2_w, self.norm2b_w = norm(), (norm() if sandwich else None)
+            self.ls2 = scale() if scaled else None
             self.mlp = make_ff(mlp, spec, device)
         else:
             self.mlp = None
@@ -221,6 +274,7 @@ class HybridLM(nn.Module):
         self.runs = layer_runs(spec.num_layers, spec.loop_start, spec.loop_stop, spec.loop_times)
         self.has_state = any(getattr(l.mixer, "uses_state", not l.mixer.uses_pages) for l in self.layers)
         self.has_pages = any(l.mixer.uses_pages for l in self.layers)
+        self.needs_tok_seq = any(getattr(l.mixer, "needs_tok_seq", False) for l in self.layers)
         self.trace: Optional[list] = None     # debugging: when a list, the stream after every layer run is appended
 
     # -- what the runner asks ---------------------------------------------------------------------
@@ -239,6 +293,8 @@ class HybridLM(nn.Module):
         spec, eps, dt = self.spec, self.spec.rms_eps, self.spec.dtype
         if spec.block == "postnorm":
             return self._forward_postnorm(inp, cache), None
+        if spec.block == "branchnorm":
+            return self._forward_branchnorm(inp, cache), None
         x0 = Fn.embedding_scaled(inp.tokens, self.embed_w, spec.embed_scale)
         x = x0.clone() if any(a for _, a in self.runs) else x0
         n = len(self.runs)
@@ -275,6 +331,32 @@ class HybridLM(nn.Module):
             if self.trace is not None:
                 self.trace.append(x.clone())
         return Fn.resid_norm(x, None, None, None, self.final_norm_w, eps, dt)
+
+    def _forward_branchnorm(self, inp, cache):
+        """x += ls * rms(f(x)) * n per sublayer; f reads the stream itself (rounded to the compute dtype). The last
+        sublayer's update also applies the final norm."""
+        spec, eps, dt = self.spec, self.spec.rms_eps, self.spec.dtype
+        x = Fn.embedding_scaled(inp.tokens, self.embed_w, spec.embed_scale)
+        n = len(self.runs)
+        if n == 0:
+            return Fn.resid_norm(x, None, None, None, self.final_norm_w, eps, dt)
+        h = x if dt == torch.float32 else x.to(dt)       # exact: the table holds compute-dtype values
+        for r, (li, _) in enumerate(self.runs):
+            L = self.layers[li]
+            last = r + 1 == n and self.trace is None
+            y = L.mixer(inp, h, cache, r)
+            if L.mlp is not None:
+                h = Fn.resid_norm(x, y, L.norm1_w, None, None, eps, dt, True, L.ls1)
+                y = L.mlp(h)
+                w_post, ls = L.norm2_w, L.ls2
+            else:
+                w_post, ls = L.norm1_w, L.ls1
+            h = Fn.resid_norm(x, y, w_post, None, self.final_norm_w if last else None, eps, dt, not last, ls)
+            if self.trace is not None:
+                self.trace.append(x.clone())
+        if self.trace is not None:
+            h = Fn.resid_norm(x, None, None, None, self.final_norm_w, eps, dt)
+        return h
 
     def compute_logits(self, inp, hidden, tpc=None, all_rows: bool = False, local: bool = False):
         rows = hidden if all_rows else hidden.index_select(0, inp.logits_idx.long())
@@ -350,12 +432,27 @@ class HybridLM(nn.Module):
                 put(m.o_w, reader.get(mp + "o"))
             elif isinstance(m, CoreMixer):
                 m.load(reader, mp, put)
+            elif isinstance(m, (RGLRUMixer, LatentAttention)):
+                m.load(reader, mp, put)
+            if L.ls1 is not None:
+                put(L.ls1, reader.get(pre + "ls1").float())
             if L.mlp is not None:
                 put(L.norm2_w, reader.get(pre + "norm2"))
                 if L.norm2b_w is not None:
                     put(L.norm2b_w, reader.get(pre + "norm2b"))
                 f = L.mlp
-                if isinstance(f, SelectedSoftmaxMoE):
+                if L.ls2 is not None:
+                    put(L.ls2, reader.get(pre + "ls2").float())
+                if isinstance(f, GroupedGLUMoE):
+                    put(f.router_w, reader.get(pre + "mlp.router"))
+                    put(f.correction, reader.get(pre + "mlp.correction").float())
+                    for e in range(f.num_experts):
+                        ep = f"{pre}mlp.e{e}."
+                        f.load_expert(e, reader.get(ep + "gate"), reader.get(ep + "up"), reader.get(ep + "down"))
+                    if f.shared is not None:
+                        sp = pre + "mlp.shared."
+                        f.shared.load(reader.get(sp + "gate"), reader.get(sp + "up"), reader.get(sp + "down"))
+                elif isinstance(f, SelectedSoftmaxMoE):
                     put(f.router_w, reader.get(pre + "mlp.router"))
                     for e in range(f.num_experts):
                         ep = f"{pre}mlp.e{e}."
@@ -379,3 +476,7 @@ def build_saritar(cfg, device):
 
 def build_femolix(cfg, device):
     return HybridLM(spec_femolix(cfg), device)
+
+
+def build_bevovik(cfg, device):
+    return HybridLM(spec_bevovik(cfg), device)

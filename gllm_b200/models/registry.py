@@ -4,7 +4,7 @@ Supported `architectures[0]` values:
   LlamaForCausalLM, Qwen2ForCausalLM, Qwen3ForCausalLM, Qwen2MoeForCausalLM, Qwen3MoeForCausalLM,
   MixtralForCausalLM, ChatGLMModel / ChatGLMForConditionalGeneration, DeepseekV2ForCausalLM,
   DeepseekV3ForCausalLM, Qwen2_5_VLForConditionalGeneration, Qwen3VLForConditionalGeneration,
-  Qwen3VLMoeForConditionalGeneration, Saritar and Femolix (layer-list decoders, models/hybrid.py).
+  Qwen3VLMoeForConditionalGeneration, Saritar, Femolix and Bevovik (layer-list decoders, models/hybrid.py).
 """
 from __future__ import annotations
 
@@ -166,6 +166,11 @@ def _build_saritar(cfg, device):
     return build_saritar(cfg, device)
 
 
+def _build_bevovik(cfg, device):
+    from gllm_b200.models.hybrid import build_bevovik
+    return build_bevovik(cfg, device)
+
+
 def _build_femolix(cfg, device):
     from gllm_b200.models.hybrid import build_femolix
     return build_femolix(cfg, device)
@@ -174,6 +179,7 @@ def _build_femolix(cfg, device):
 ARCHITECTURES: Dict[str, Callable] = {
     "Saritar": _build_saritar,
     "Femolix": _build_femolix,
+    "Bevovik": _build_bevovik,
     "LlamaForCausalLM": _build_decoder(spec_llama),
     "MistralForCausalLM": _build_decoder(spec_llama),
     "Qwen2ForCausalLM": _build_decoder(spec_qwen2),
@@ -189,6 +195,17 @@ ARCHITECTURES: Dict[str, Callable] = {
     "Qwen3VLForConditionalGeneration": _build_qwen3_vl,
     "Qwen3VLMoeForConditionalGeneration": _build_qwen3_vl,
 }
+
+
+def complete_config(cfg: HFConfig, reader) -> None:
+    """Sizes that a config leaves to the checkpoint's tensor shapes are written into `cfg` before the model is
+    built (`reader` is None for random weights: defaults apply). Bevovik: the rank of a `gla` mixer's decay
+    projection is the row count of `l<i>.mix.a1`."""
+    if cfg["architectures"][0] == "Bevovik":
+        for i, layer in enumerate(cfg.get("layers") or []):
+            m = layer.get("mixer") or {}
+            if layer.get("type") == "gla" and "low_rank" not in m:
+                m["low_rank"] = int(reader.shape(f"l{i}.mix.a1")[0]) if reader is not None else 16
 
 
 def build_model(cfg: HFConfig, device):

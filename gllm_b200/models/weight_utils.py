@@ -154,6 +154,15 @@ class CheckpointReader:
             return self._bin[key]
         return self._handle(self._files[key]).get_tensor(key)
 
+    def shape(self, name: str):
+        """Shape of a tensor without reading its data (sizes that a config leaves to the checkpoint)."""
+        key = self.resolve(name)
+        if key is None:
+            raise KeyError(f"tensor {name} not found in checkpoint {self.path}")
+        if key in self._bin:
+            return tuple(self._bin[key].shape)
+        return tuple(self._handle(self._files[key]).get_slice(key).get_shape())
+
     def get(self, name: str) -> torch.Tensor:
         """Tensor by name. Block-quantised fp8 weights (`<name>` e4m3 + `<name>_scale_inv` fp32 per
         128x128 block — DeepSeek-V3 / Qwen3-FP8 checkpoints, reference: gllm/layers/linear.py:68-112)

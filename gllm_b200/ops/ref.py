@@ -465,15 +465,21 @@ def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> to
 
 
 def resid_norm(x: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torch.Tensor],
-               add: Optional[torch.Tensor], w_pre: Optional[torch.Tensor], eps: float, out_dtype):
+               add: Optional[torch.Tensor], w_pre: Optional[torch.Tensor], eps: float, out_dtype,
+               emit_plain: bool = False, post_scale: Optional[torch.Tensor] = None):
     """In place on the fp32 stream x [T, W]:  x += rms(y) * w_post ;  x += add ;  returns rms(x) * w_pre cast to
-    `out_dtype` (None when w_pre is None). Every step is optional. All arithmetic in fp32."""
+    `out_dtype` (None when w_pre is None). Every step is optional. All arithmetic in fp32. `post_scale` [W] fp32
+    (a layer scale) multiplies the normed branch element by element: x += rms(y) * w_post * post_scale. `emit_plain` (with w_pre None): returns the stream itself rounded to
+    `out_dtype` — x for fp32 — for sublayers that read the stream without a norm in front."""
     if y is not None:
         yf = y.float()
-        x += yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + eps) * w_post.float()
+        br = yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + eps) * w_post.float()
+        x += br * post_scale.float() if post_scale is not None else br
     if add is not None:
         x += add
     if w_pre is None:
+        if emit_plain:
+            return x if out_dtype == torch.float32 else x.to(out_dtype)
         return None
     return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w_pre.float()).to(out_dtype)
 
@@ -548,12 +554,17 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
 
 def causal_conv_silu(xz: torch.Tensor, channels: int, w: torch.Tensor, b: torch.Tensor,
                      conv_state: Optional[torch.Tensor], rec_slots: Optional[torch.Tensor], seq_lens: torch.Tensor,
-                     query_start_loc: torch.Tensor) -> torch.Tensor:
+                     query_start_loc: torch.Tensor, act: str = "silu", in_bias: Optional[torch.Tensor] = None,
+                     out_dtype=None) -> torch.Tensor:
     """Depthwise causal convolution + SiLU over the first `channels` columns of xz [T, >= channels], per sequence.
     w [channels, taps] (last tap = current token), b [channels]. conv_state [slots, taps - 1, channels] holds the
-    last taps - 1 inputs of every sequence; a sequence whose chunk starts at position 0 starts from zeros."""
+    last taps - 1 inputs of every sequence; a sequence whose chunk starts at position 0 starts from zeros.
+    `act`: "silu" | "none". `in_bias` [channels] fp32 is added to every input that exists (the zeros before the
+    start of a sequence stay zeros); the carried state holds the inputs without it. `out_dtype`: the result's type
+    (default: that of xz)."""
     taps = w.shape[1]
-    out = torch.empty(xz.shape[0], channels, dtype=xz.dtype, device=xz.device)
+    odt = out_dtype or xz.dtype
+    out = torch.empty(xz.shape[0], channels, dtype=odt, device=xz.device)
     qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
     for s in range(len(sl)):
         q0, q1 = qsl[s], qsl[s + 1]
@@ -562,13 +573,18 @@ def causal_conv_silu(xz: torch.Tensor, channels: int, w: torch.Tensor, b: torch.
             continue
         x = xz[q0:q1, :channels].float()
         hist = torch.zeros(taps - 1, channels, dtype=torch.float32, device=xz.device)
+        have = min(sl[s] - n, taps - 1)              # carried inputs that exist (the rest precede position 0)
         if conv_state is not None and sl[s] - n > 0:
             hist = conv_state[int(rec_slots[s])][: taps - 1].float()
         xp = torch.cat([hist, x], 0)
+        xin = xp
+        if in_bias is not None:
+            xin = xp + in_bias.float()
+            xin[: taps - 1 - max(have, 0)] = 0.0
         acc = b.float().expand(n, channels).clone()
         for j in range(taps):
-            acc = acc + xp[j:j + n] * w[:, j].float()
-        out[q0:q1] = F.silu(acc).to(xz.dtype)
+            acc = acc + xin[j:j + n] * w[:, j].float()
+        out[q0:q1] = (F.silu(acc) if act == "silu" else acc).to(odt)
         if conv_state is not None and taps > 1:
             conv_state[int(rec_slots[s])] = xp[n:].to(conv_state.dtype)
     return out
@@ -663,9 +679,12 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: O
                       a: Optional[torch.Tensor], neg_a: Optional[torch.Tensor], dt_bias: Optional[torch.Tensor],
                       decay: Optional[torch.Tensor], state: Optional[torch.Tensor], rec_slots, seq_lens, query_start_loc,
                       heads: int, qk_heads: int, dim: int, v_dim: int, silu_in: bool, unit_qk: bool, q_scale: float,
-                      delta: bool) -> torch.Tensor:
+                      delta: bool, zk: Optional[torch.Tensor] = None, zk_bias: Optional[torch.Tensor] = None,
+                      inv_tau: float = 1.0) -> torch.Tensor:
     """Matrix-state recurrence per head, fp32, token by token, S [dim, v_dim]:
-        g = exp(neg_a[h] * softplus(a + dt_bias[h]))   (or the constant decay[h])
+        g = exp(neg_a[h] * softplus(a + dt_bias[h]))   (or the constant decay[h]; or, with `zk` [T, heads * dim]
+            and `zk_bias` [heads * dim], one decay per key channel, g[d] = sigmoid(zk + zk_bias)^inv_tau, acting
+            on row d of S)
         S <- g S;   u = beta * (v - S^T k) with `delta`, else u = v;   S <- S + k u^T;   o = S^T q
     q, k [T, qk_heads * dim] (head h reads group h // (heads / qk_heads)), v [T, heads * v_dim], beta / a [T, heads].
     `silu_in`: q, k, v pass SiLU first; `unit_qk`: q and k are scaled to unit length (1e-6 inside the root);
@@ -690,7 +709,10 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: O
             kk = kk / torch.sqrt((kk * kk).sum(-1, keepdim=True) + 1e-6)
         qq = (qq * q_scale).repeat_interleave(rep, 1)
         kk = kk.repeat_interleave(rep, 1)
-        if decay is not None:
+        if zk is not None:
+            zz = zk[q0:q1].float() + (zk_bias.float() if zk_bias is not None else 0.0)
+            g = torch.exp(F.logsigmoid(zz) * inv_tau).reshape(n, heads, dim, 1)
+        elif decay is not None:
             g = decay.float().view(1, heads).expand(n, heads)
         else:
             g = torch.exp(neg_a.float() * F.softplus(a[q0:q1].float() + dt_bias.float()))
@@ -700,7 +722,7 @@ def linear_state_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: O
             st = state[int(rec_slots[s])].clone()
         o = torch.empty(n, heads, v_dim, dtype=torch.float32, device=q.device)
         for i in range(n):
-            st = st * g[i].view(heads, 1, 1)
+            st = st * (g[i] if zk is not None else g[i].view(heads, 1, 1))
             u = vv[i]
             if delta:
                 u = b[i].view(heads, 1) * (u - torch.einsum("hdv,hd->hv", st, kk[i]))
@@ -745,3 +767,205 @@ def router_topk(h: torch.Tensor, w: torch.Tensor, top_k: int):
 
 def softcap(z: torch.Tensor, cap: float) -> torch.Tensor:
     return (cap * torch.tanh(z.float() / cap)).to(z.dtype)
+
+
+# ----------------------------------------------------------------------------------------------
+# branch-norm blocks with layer scale, key-channel-decay linear attention, latent attention with pair-wise (YaRN)
+# rotary, the real-gated linear recurrent unit, grouped routing with identity experts, clamped gated experts
+# (PyTorch forms of csrc/seq/latent_ops.cu)
+# ----------------------------------------------------------------------------------------------
+def block_linear(x: torch.Tensor, w: torch.Tensor, out_dtype=None) -> torch.Tensor:
+    """Block-diagonal linear map: x [T, B * K] is cut into B parts, part b times w[b] [N, K] ([out, in]);
+    -> [T, B * N] in `out_dtype` (default: that of x), fp32 accumulation."""
+    t = x.shape[0]
+    nb, n, k = w.shape
+    y = torch.einsum("tbk,bnk->tbn", x.float().reshape(t, nb, k), w.float()).reshape(t, nb * n)
+    return y.to(out_dtype or x.dtype)
+
+
+def rglru_scan(u: torch.Tensor, gates: torch.Tensor, gate_bias: torch.Tensor, c_decay: torch.Tensor,
+               y_pre: torch.Tensor, y_bias: torch.Tensor, state: Optional[torch.Tensor], rec_slots, seq_lens,
+               query_start_loc, block: int, out_dtype) -> torch.Tensor:
+    """Real-gated linear recurrent unit, one fp32 state per channel, token by token:
+        r = sigmoid(gate_r + bias_r);  i = sigmoid(gate_i + bias_i)
+        a = exp(c_decay * r);  S <- a S + sqrt(1 - a^2) * i * u;  out = S * gelu_tanh(y_pre + y_bias)
+    u [T, C]; gates [T, 2C] (any float type) and gate_bias [2C] are laid out per block of `block` channels as
+    [r of the block | i of the block] (the result of one block-diagonal product with stacked weights);
+    c_decay [C] fp32 (negative), y_pre [T, C] (any row stride). state
+    [slots, 1, C] fp32 carries S between chunks (zeros for a chunk that starts at position 0, also for its first
+    token)."""
+    t, c = u.shape
+    out = torch.empty(t, c, dtype=out_dtype, device=u.device)
+    qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    gz = (gates.float() + gate_bias.float()).reshape(t, c // block, 2, block)
+    r = torch.sigmoid(gz[:, :, 0]).reshape(t, c)
+    ig = torch.sigmoid(gz[:, :, 1]).reshape(t, c)
+    log_a = c_decay.float() * r
+    a = torch.exp(log_a)
+    b = torch.sqrt(-torch.expm1(2.0 * log_a)) * ig * u.float()
+    z = y_pre[:, :c].float() + y_bias.float()
+    y = 0.5 * z * (1.0 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z * z * z)))
+    for s in range(len(sl)):
+        q0, q1 = qsl[s], qsl[s + 1]
+        n = q1 - q0
+        if n <= 0:
+            continue
+        st = torch.zeros(c, dtype=torch.float32, device=u.device)
+        if state is not None and sl[s] - n > 0:
+            st = state[int(rec_slots[s])].reshape(-1)[:c].clone()
+        for i in range(q0, q1):
+            st = a[i] * st + b[i]
+            out[i] = (st * y[i]).to(out_dtype)
+        if state is not None:
+            state[int(rec_slots[s])].reshape(-1)[:c] = st
+    return out
+
+
+def pair_rotary_frequencies(dims: int, base: float, scaling: Optional[dict] = None):
+    """-> (fp32 frequency per pair [dims / 2], factor on cos and sin). Pair i turns by position * base^(-2i/dims);
+    with YaRN `scaling` {factor, original, fast, slow}: where(t) = dims ln(original / (2 pi t)) / (2 ln base),
+    lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo,
+    0.001), 0, 1), frequency f_i / factor * ramp_i + f_i (1 - ramp_i), magnitude 0.1 ln(factor) + 1."""
+    i = torch.arange(dims // 2, dtype=torch.float64)
+    f = torch.exp(-(2.0 * i / dims) * math.log(base))
+    mag = 1.0
+    if scaling:
+        factor, orig = float(scaling["factor"]), float(scaling["original"])
+
+        def where(turns):
+            return dims * math.log(orig / (2.0 * math.pi * turns)) / (2.0 * math.log(base))
+
+        lo = max(math.floor(where(float(scaling["fast"]))), 0)
+        hi = min(math.ceil(where(float(scaling["slow"]))), dims - 1)
+        ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
+        f = f / factor * ramp + f * (1.0 - ramp)
+        mag = 0.1 * math.log(factor) + 1.0
+    return f.float(), float(mag)
+
+
+def rotate_adjacent_pairs(x: torch.Tensor, positions: torch.Tensor, freqs: torch.Tensor, mag: float) -> torch.Tensor:
+    """x [T, ..., D] fp32: entries 2i and 2i + 1 (i < len(freqs)) turn by the fp32 angle positions * freqs[i], cos
+    and sin times `mag`; later entries pass through."""
+    n = freqs.shape[0]
+    if n == 0:
+        return x
+    ang = positions.to(torch.float32)[:, None] * freqs.to(torch.float32)[None, :]
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [n]
+    c, s = (torch.cos(ang) * mag).reshape(shape), (torch.sin(ang) * mag).reshape(shape)
+    a, b = x[..., 0:2 * n:2], x[..., 1:2 * n:2]
+    out = x.clone()
+    out[..., 0:2 * n:2] = a * c - b * s
+    out[..., 1:2 * n:2] = b * c + a * s
+    return out
+
+
+def rms_rows(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
+    """RMS norm of every row of x [T, n] (any row stride) times w [n]; fp32 arithmetic, result in x's dtype."""
+    xf = x.float()
+    return (xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps) * w.float()).to(x.dtype)
+
+
+def linear_batched(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+    """out[:, b, :] = a[:, b, :] @ w[b].T for every b: a [T, B, K] and out [T, B, N] may be strided views."""
+    out.copy_(torch.einsum("tbk,bnk->tbn", a.float(), w.float()).to(out.dtype))
+    return out
+
+
+def latent_norm_rope_write(q: torch.Tensor, dkv: torch.Tensor, rank: int, rot: int, norm_w: torch.Tensor, eps: float,
+                           positions: torch.Tensor, freqs: torch.Tensor, mag: float, q_full: torch.Tensor,
+                           cache: Optional[torch.Tensor], slots: Optional[torch.Tensor]):
+    """Latent attention, between the projections and the attention: q [T, H, dim + rot] (view) — its last `rot`
+    entries per head are rotated into q_full[:, :, rank:] (q_full [T, H, rank + rot]; the first `rank` columns are
+    the caller's: the absorbed queries). dkv [T, rank + rot]: the first `rank` columns are RMS-normed with norm_w
+    (the latent), the last `rot` rotated (the key part all heads share); the row [latent | rotated key] goes to
+    the paged latent cache [pages, 1, (rank + rot) / slab, page, slab] at `slots`. Norm, angles and rotation in
+    fp32."""
+    t, h = q.shape[0], q.shape[1]
+    dim = q.shape[2] - rot
+    q_full[:, :, rank:] = rotate_adjacent_pairs(q[:, :, dim:].float(), positions, freqs, mag).to(q_full.dtype)
+    c = dkv[:, :rank].float()
+    c = c * torch.rsqrt((c * c).mean(-1, keepdim=True) + eps) * norm_w.float()
+    kr = rotate_adjacent_pairs(dkv[:, rank:rank + rot].float(), positions, freqs, mag)
+    if cache is not None:
+        _cache_rows_write(cache, slots, torch.cat([c, kr], -1).to(cache.dtype).reshape(t, 1, rank + rot))
+
+
+def latent_attention(q_full: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, seq_lens: torch.Tensor,
+                     query_start_loc: torch.Tensor, scale: float, rank: int) -> torch.Tensor:
+    """Causal multi-query attention over the paged latent cache: every head's query q_full [T, H, rank + rot]
+    meets the one shared key row [latent | rotated key]; the values are the row's first `rank` columns.
+    -> out [T, H, rank] in q_full's dtype. Scores and softmax in fp32."""
+    t, h, d = q_full.shape
+    out = torch.zeros(t, h, rank, dtype=q_full.dtype, device=q_full.device)
+    qsl, sl = query_start_loc.tolist(), seq_lens.tolist()
+    for s in range(len(sl)):
+        q0, q1 = qsl[s], qsl[s + 1]
+        ql = q1 - q0
+        if ql <= 0:
+            continue
+        lat = gather_kv(cache, block_table[s], sl[s])[:, 0].float()            # [L, rank + rot]
+        att = torch.einsum("qhd,kd->hqk", q_full[q0:q1].float(), lat) * scale
+        qi = torch.arange(ql, device=q_full.device).view(ql, 1) + (sl[s] - ql)
+        kj = torch.arange(sl[s], device=q_full.device).view(1, sl[s])
+        att = att.masked_fill((kj > qi).unsqueeze(0), float("-inf"))
+        out[q0:q1] = torch.einsum("hqk,kd->qhd", torch.softmax(att, -1), lat[:, :rank]).to(q_full.dtype)
+    return out
+
+
+def grouped_router(h: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top_k: int, n_groups: int,
+                   keep_groups: int, scale: float):
+    """fp32 router: scores = softmax(h . w^T) over all outputs; choice = scores + correction; outputs form
+    `n_groups` equal groups of neighbours, a group's score is its largest choice score and only the best
+    `keep_groups` groups stay eligible (the others count as -inf); the top_k largest eligible choice scores are
+    chosen (ties: the lower index); weights = chosen scores / (their sum + 1e-20) * scale.
+    -> (weights fp32 [T, k], ids int32 [T, k])"""
+    sc = torch.softmax(h.float() @ w.float().t(), -1)
+    choice = sc + correction.float() if correction is not None else sc
+    t, n = sc.shape
+    if n_groups > 1:
+        per = n // n_groups
+        best = choice.reshape(t, n_groups, per).max(-1).values
+        kept = torch.topk(best, keep_groups, dim=-1).indices
+        ok = torch.zeros(t, n_groups, dtype=torch.bool, device=h.device).scatter_(1, kept, True)
+        choice = choice.masked_fill(~ok.repeat_interleave(per, 1), float("-inf"))
+    ids = torch.topk(choice, top_k, dim=-1).indices
+    sel = sc.gather(1, ids)
+    return sel / (sel.sum(-1, keepdim=True) + 1e-20) * scale, ids.to(torch.int32)
+
+
+def glu_clamp(gu: torch.Tensor, limit: float, alpha: float = 1.702) -> torch.Tensor:
+    """gu [T, 2F] = [gate | up] -> g sigmoid(alpha g) (u + 1) with g = min(gate, limit), u = clamp(up, +-limit)."""
+    f = gu.shape[1] // 2
+    g = gu[:, :f].float().clamp(max=limit)
+    u = gu[:, f:].float().clamp(-limit, limit)
+    return (g * torch.sigmoid(alpha * g) * (u + 1.0)).to(gu.dtype)
+
+
+def linear_glu_clamp(x: torch.Tensor, w_interleaved: torch.Tensor, limit: float, alpha: float = 1.702,
+                     block: int = 128) -> torch.Tensor:
+    """`glu_clamp` of x @ w^T for a weight whose gate / up rows are interleaved per `block`."""
+    y = F.linear(x, w_interleaved)
+    t, two_i = y.shape
+    y = y.reshape(t, two_i // (2 * block), 2, block)
+    gu = torch.cat([y[:, :, 0].reshape(t, -1), y[:, :, 1].reshape(t, -1)], 1)
+    return glu_clamp(gu, limit, alpha)
+
+
+def routed_glu_experts(h: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, weights: torch.Tensor, ids: torch.Tensor,
+                       limit: float, alpha: float = 1.702) -> torch.Tensor:
+    """sum_k weights[t, k] * expert_{ids[t, k]}(h[t]) with clamped gated experts (`glu_clamp` between the two
+    products); an id >= the number of experts names an identity expert, whose result is h[t] itself.
+    w13 [E, 2F, W] = [gate rows ; up rows], w2 [E, W, F]."""
+    e_real = w13.shape[0]
+    out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+    for kk in range(ids.shape[1]):
+        for e in ids[:, kk].unique().tolist():
+            rows = (ids[:, kk] == e).nonzero().flatten()
+            x = h[rows]
+            if e >= e_real:
+                y = x.float()
+            else:
+                a = glu_clamp(linear(x, w13[e]), limit, alpha)
+                y = linear(a, w2[e]).float()
+            out[rows] += weights[rows, kk].float().unsqueeze(1) * y
+    return out.to(h.dtype)
