@@ -60,6 +60,9 @@ struct GemmParams {
   // instead of a cuBLAS bmm (reference: gllm/layers/attention.py:463-484).
   int batch, rows_per_batch;
   int64_t c_batch_stride;
+  // gated epilogue variant (kEpiSiluMul with glu_limit > 0): g = min(gate, limit), u = clamp(up, +-limit),
+  // out = g * sigmoid(glu_alpha * g) * (u + 1) instead of silu(gate) * up
+  float glu_limit, glu_alpha;
   // split-K (decode-sized M): unit = (tile, k-slice); partials go through an fp32 workspace in a
   // thread-private layout, the last-arriving CTA of a tile sums them in slice order and runs the epilogue
   int split_k;
@@ -418,7 +421,13 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
               for (int e = 0; e < 8; ++e) {
                 const float gv = __uint_as_float(g[j + e]);
                 const float uv = __uint_as_float(u[j + e]);
-                f[e] = gv / (1.0f + __expf(-gv)) * uv;
+                if (p.glu_limit > 0.f) {
+                  const float gc = fminf(gv, p.glu_limit);
+                  const float uc = fminf(fmaxf(uv, -p.glu_limit), p.glu_limit);
+                  f[e] = gc / (1.0f + __expf(-p.glu_alpha * gc)) * (uc + 1.0f);
+                } else {
+                  f[e] = gv / (1.0f + __expf(-gv)) * uv;
+                }
               }
               stage_put((h + j) / 8, f);
             }
@@ -604,10 +613,10 @@ GLLM_EXPORT int gllm_gemm_tune(int force_split, int max_split_m) {
   return 0;
 }
 
-GLLM_EXPORT int gllm_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* C,
-                               int64_t ldc, int M, int N, int K, const void* bias, int epi,
-                               int force_bn, const GemmComm* comm, void* ws, int64_t ws_bytes, void* tile_cnt,
-                               int max_tiles, void* stream) {
+static int gemm_bf16_impl(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc, int M, int N,
+                          int K, const void* bias, int epi, int force_bn, const GemmComm* comm, void* ws,
+                          int64_t ws_bytes, void* tile_cnt, int max_tiles, void* stream, float glu_limit,
+                          float glu_alpha) {
   if (M <= 0 || N <= 0 || K <= 0) return 0;
   if ((K % 8) != 0 || (N % 8) != 0 || (lda % 8) != 0 || (ldw % 8) != 0 || (ldc % 8) != 0) {
     fprintf(stderr, "[gllm_b200] gemm_bf16: K, N and leading dims must be multiples of 8\n");
@@ -627,6 +636,8 @@ GLLM_EXPORT int gllm_gemm_bf16(const void* A, int64_t lda, const void* W, int64_
   p.C = reinterpret_cast<__nv_bfloat16*>(C);
   p.ldc = static_cast<int>(ldc);
   p.bias = reinterpret_cast<const __nv_bfloat16*>(bias);
+  p.glu_limit = glu_limit;
+  p.glu_alpha = glu_alpha;
   if (comm != nullptr) {
     p.a_ready = comm->a_ready;
     p.a_expected = comm->a_expected;
@@ -657,6 +668,24 @@ GLLM_EXPORT int gllm_gemm_bf16(const void* A, int64_t lda, const void* W, int64_
       return 1;
   }
 #undef DISPATCH
+}
+
+GLLM_EXPORT int gllm_gemm_bf16(const void* A, int64_t lda, const void* W, int64_t ldw, void* C,
+                               int64_t ldc, int M, int N, int K, const void* bias, int epi,
+                               int force_bn, const GemmComm* comm, void* ws, int64_t ws_bytes, void* tile_cnt,
+                               int max_tiles, void* stream) {
+  return gemm_bf16_impl(A, lda, W, ldw, C, ldc, M, N, K, bias, epi, force_bn, comm, ws, ws_bytes, tile_cnt, max_tiles,
+                        stream, 0.f, 0.f);
+}
+
+// Gate / up projection with the clamped gated epilogue (weight rows interleaved per 128, BN = 256):
+// C[:, f] = g sigmoid(alpha g) (u + 1), g = min(gate, limit), u = clamp(up, +-limit).
+GLLM_EXPORT int gllm_gemm_bf16_glu(const void* A, int64_t lda, const void* W, int64_t ldw, void* C, int64_t ldc,
+                                   int M, int N, int K, float limit, float alpha, void* ws, int64_t ws_bytes,
+                                   void* tile_cnt, int max_tiles, void* stream) {
+  if (limit <= 0.f) return 1;
+  return gemm_bf16_impl(A, lda, W, ldw, C, ldc, M, N, K, nullptr, kEpiSiluMul, 256, nullptr, ws, ws_bytes, tile_cnt,
+                        max_tiles, stream, limit, alpha);
 }
 
 // Number of (m_tile, n_tile) pairs whose rows intersect [row0, row1) — used by the consumer
@@ -702,9 +731,9 @@ GLLM_EXPORT int gllm_gemm_bf16_batched(const void* A, int64_t lda_t, int64_t lda
 // Grouped (MoE) GEMM: rows of A are expert-sorted and padded to 128-row tiles; tile t uses the weight
 // slab W[tile_expert[t]] ([E, N, K] contiguous). The live tile count is read on the device.
 // epi: 0 store, 1 SiLU-gate (slab rows interleaved per 64 like the dense gate/up weight).
-GLLM_EXPORT int gllm_moe_grouped_gemm(const void* A, int64_t lda, const void* W, void* C, int64_t ldc,
-                                      int max_tiles, int N, int K, int E, const void* tile_expert,
-                                      const void* num_tiles_ptr, int epi, const void* row_dest, void* stream) {
+static int moe_grouped_gemm_impl(const void* A, int64_t lda, const void* W, void* C, int64_t ldc, int max_tiles, int N,
+                                 int K, int E, const void* tile_expert, const void* num_tiles_ptr, int epi,
+                                 const void* row_dest, void* stream, float glu_limit, float glu_alpha) {
   if (max_tiles <= 0) return 0;
   if ((K % 8) != 0 || (N % 8) != 0 || (lda % 8) != 0 || (ldc % 8) != 0) return 1;
   const int bn = 128;  // 64|64 gate/up interleave for the SiLU epilogue; good balance for expert tiles
@@ -722,6 +751,24 @@ GLLM_EXPORT int gllm_moe_grouped_gemm(const void* A, int64_t lda, const void* W,
   p.num_m_tiles_ptr = reinterpret_cast<const int32_t*>(num_tiles_ptr);
   p.n_per_expert = N;
   p.row_dest = reinterpret_cast<const int64_t*>(row_dest);
+  p.glu_limit = glu_limit;
+  p.glu_alpha = glu_alpha;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   return epi == kEpiSiluMul ? launch_gemm<128, kEpiSiluMul>(ta, tb, p, st) : launch_gemm<128, kEpiStore>(ta, tb, p, st);
+}
+
+GLLM_EXPORT int gllm_moe_grouped_gemm(const void* A, int64_t lda, const void* W, void* C, int64_t ldc,
+                                      int max_tiles, int N, int K, int E, const void* tile_expert,
+                                      const void* num_tiles_ptr, int epi, const void* row_dest, void* stream) {
+  return moe_grouped_gemm_impl(A, lda, W, C, ldc, max_tiles, N, K, E, tile_expert, num_tiles_ptr, epi, row_dest,
+                               stream, 0.f, 0.f);
+}
+
+// Grouped gate / up GEMM with the clamped gated epilogue (slab rows interleaved per 64).
+GLLM_EXPORT int gllm_moe_grouped_gemm_glu(const void* A, int64_t lda, const void* W, void* C, int64_t ldc,
+                                          int max_tiles, int N, int K, int E, const void* tile_expert,
+                                          const void* num_tiles_ptr, float limit, float alpha, void* stream) {
+  if (limit <= 0.f) return 1;
+  return moe_grouped_gemm_impl(A, lda, W, C, ldc, max_tiles, N, K, E, tile_expert, num_tiles_ptr, kEpiSiluMul, nullptr,
+                               stream, limit, alpha);
 }

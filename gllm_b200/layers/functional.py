@@ -265,9 +265,11 @@ def linear_batched(a, w, out):
 
 def rglru_scan(u, gates, gate_bias, c_decay, y_pre, y_bias, state, inp, block, out_dtype):
     slots = inp.rec_slots if state is not None else None
-    fn = _lat().rglru_scan if u.is_cuda else ref.rglru_scan
-    return fn(u, gates, gate_bias, c_decay, y_pre, y_bias, state, slots, inp.seq_lens, inp.query_start_loc, block,
-              out_dtype)
+    if u.is_cuda:
+        return _lat().rglru_scan(u, gates, gate_bias, c_decay, y_pre, y_bias, state, slots, inp.seq_lens,
+                                 inp.query_start_loc, block, out_dtype, max_q_len=getattr(inp, "max_q_len", None))
+    return ref.rglru_scan(u, gates, gate_bias, c_decay, y_pre, y_bias, state, slots, inp.seq_lens,
+                          inp.query_start_loc, block, out_dtype)
 
 
 def latent_norm_rope_write(q, dkv, rank, rot, norm_w, eps, positions, freqs, mag, q_full, cache, slots):
@@ -298,8 +300,8 @@ def linear_glu_clamp(x, w_interleaved, limit, alpha=1.702):
     return ref.linear_glu_clamp(x, w_interleaved, limit, alpha)
 
 
-def routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha=1.702):
-    """Clamped gated experts; ids >= the number of experts are identity experts."""
+def routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha=1.702, n_all=None):
+    """Clamped gated experts; ids >= the number of experts are identity experts (n_all: experts + identity)."""
     if h.is_cuda:
-        return _lat().routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha)
+        return _lat().routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha, n_all)
     return ref.routed_glu_experts(h, w13, w2, weights, ids, limit, alpha)

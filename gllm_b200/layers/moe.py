@@ -325,7 +325,7 @@ class GroupedGLUMoE(nn.Module):
         w, ids = Fn.grouped_router(h, self.router_w, self.correction, self.top_k, self.n_groups, self.keep_groups,
                                    self.scale)
         out = Fn.routed_glu_experts(h, self.w13[: self.num_experts], self.w2[: self.num_experts], w, ids, self.limit,
-                                    self.interleaved, self.alpha)
+                                    self.interleaved, self.alpha, self.num_experts + self.identity)
         if self.shared is not None:
             out = out + self.shared(h)
         return out

@@ -365,7 +365,14 @@ class HybridLM(nn.Module):
 
     # -- weights ----------------------------------------------------------------------------------
     def process_weights(self):
-        pass
+        """After the weights are final and before any CUDA-graph capture: workspaces whose addresses captured graphs
+        keep (the split-KV partials of the tensor-core latent attention)."""
+        if self.device.type == "cuda" and self.spec.dtype == torch.bfloat16:
+            for L in self.layers:
+                m = L.mixer
+                if isinstance(m, LatentAttention) and m.kv_rank == 512 and m.rot_dim == 64:
+                    from gllm_b200.ops import sm100
+                    sm100._mla_workspace(self.device, m.heads)
 
     def init_dummy(self, seed: int = 0):
         g = torch.Generator(device="cpu").manual_seed(seed)

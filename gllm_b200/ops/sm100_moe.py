@@ -66,8 +66,10 @@ def grouped_topk(logits: torch.Tensor, top_k: int, renormalize: bool, n_group: i
 def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: Optional[torch.Tensor],
                   topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor] = None,
                   out: Optional[torch.Tensor] = None, n_valid: Optional[torch.Tensor] = None,
-                  row_dest_fn=None) -> Optional[torch.Tensor]:
+                  row_dest_fn=None, glu=None) -> Optional[torch.Tensor]:
     """x [T,H]; w13 [E_local, 2I, H] (gate/up rows interleaved per 64); w2 [E_local, H, I]; ids global.
+    `glu` = (limit, alpha): the first GEMM's epilogue is the clamped gated form g sigmoid(alpha g) (u + 1) with
+    g = min(gate, limit), u = clamp(up, +-limit) instead of silu(gate) * up.
 
     `n_valid` (device int32 scalar): only the first n_valid rows of x are live (EP receive pool).
     `row_dest_fn(slot_pos, rows)` -> int64 [rows] device table: GEMM2's epilogue then stores every output
@@ -93,8 +95,13 @@ def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: 
     st = stream_ptr()
     check(L.gllm_moe_align_gather(_p(topk_ids), _p(expert_map), t, k, e_local, _p(meta), _p(tile_expert), max_tiles,
                                   _p(slot_pos), _p(x), x.stride(0), _p(xs), h, _p(n_valid), st), "moe_align_gather")
-    check(L.gllm_moe_grouped_gemm(_p(xs), h, _p(w13), _p(hbuf), inter, max_tiles, two_i, h, e_local,
-                                  _p(tile_expert), _p(meta), 1, None, st), "moe_grouped_gemm1")
+    if glu is not None:
+        check(L.gllm_moe_grouped_gemm_glu(_p(xs), h, _p(w13), _p(hbuf), inter, max_tiles, two_i, h, e_local,
+                                          _p(tile_expert), _p(meta), float(glu[0]), float(glu[1]), st),
+              "moe_grouped_gemm1_glu")
+    else:
+        check(L.gllm_moe_grouped_gemm(_p(xs), h, _p(w13), _p(hbuf), inter, max_tiles, two_i, h, e_local,
+                                      _p(tile_expert), _p(meta), 1, None, st), "moe_grouped_gemm1")
     if row_dest_fn is not None:
         row_dest = row_dest_fn(slot_pos, rows)
         check(L.gllm_moe_grouped_gemm(_p(hbuf), inter, _p(w2), _p(hbuf), h, max_tiles, h, inter, e_local,

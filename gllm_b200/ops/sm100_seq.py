@@ -26,23 +26,23 @@ def _L():
         P, I, G, F = c_void_p, c_int, c_long, c_float
         sigs = {
             "gllm_seq_embed_scale": [P, P, P, I, I, I, F, I, P],
-            "gllm_seq_resid_norm": [P, P, G, P, P, P, P, I, I, F, I, P],
+            "gllm_seq_resid_norm": [P, P, G, P, P, P, P, P, I, I, F, I, I, P],
             "gllm_seq_qk_norm_kv_write": [P, G, I, I, I, I, P, P, F, P, P, P, P, I, I, I, P],
             "gllm_seq_window_attention": [P, P, P, P, I, P, P, I, I, F, I, I, I, I, I, I, P, P, G, F, I, I, I, I, P],
             "gllm_seq_postnorm": [P, P, G, P, P, I, I, F, F, I, P],
             "gllm_seq_qk_norm_rope_kv_write": [P, G, I, I, I, I, I, P, P, F, P, I, ctypes.c_double, P, P, P, P, I, I, I,
                                                I, P],
             "gllm_seq_linear_state": [P, G, P, G, P, G, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P,
-                                      I, I, P],
+                                      I, I, P, G, P, F, P],
             "gllm_seq_gated_group_norm": [P, I, P, G, P, I, I, F, I, F, P, G, I, I, P],
             "gllm_seq_silu_mul": [P, G, I, I, P, I, P],
             "gllm_seq_router_select": [P, I, I, I, P, P, P],
             "gllm_seq_router_logits": [P, G, P, I, I, I, P, I, P],
             "gllm_seq_router_logits_mma": [P, G, P, I, I, I, P, P],
             "gllm_seq_gemm_simt_f32out": [P, G, P, G, P, G, I, I, I, I, P],
-            "gllm_seq_routed_experts": [P, G, P, P, P, P, I, I, I, I, P, P, I, P],
+            "gllm_seq_routed_experts": [P, G, P, P, P, P, I, I, I, I, P, P, I, I, F, F, P],
             "gllm_seq_softcap": [P, G, I, I, F, I, P],
-            "gllm_seq_conv_silu": [P, G, I, I, I, P, P, I, P, P, P, P, P, I, P],
+            "gllm_seq_conv_silu": [P, G, I, I, I, P, P, I, P, P, P, P, P, I, I, P, P],
             "gllm_seq_selective_scan": [P, P, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, P, I, I, P],
             "gllm_seq_relu2": [P, P, G, I, P],
             "gllm_seq_gemm_simt": [P, G, P, G, P, G, I, I, I, I, P],
@@ -96,10 +96,16 @@ def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> to
     return out
 
 
-def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype):
+def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None):
     assert x.dtype == torch.float32 and x.is_contiguous()
     t, width = x.shape
-    out = torch.empty(t, width, dtype=out_dtype, device=x.device) if w_pre is not None else None
+    plain = bool(emit_plain) and w_pre is None
+    if plain and out_dtype == torch.float32:
+        plain, ret_x = False, True          # the fp32 stream is its own copy
+    else:
+        ret_x = False
+    out = torch.empty(t, width, dtype=out_dtype, device=x.device) if (w_pre is not None or plain) else None
+    assert post_scale is None or (post_scale.dtype == torch.float32 and post_scale.is_contiguous())
     ref_t = w_pre if w_pre is not None else (w_post if w_post is not None else None)
     is32 = 1 if (ref_t is not None and ref_t.dtype == torch.float32) or (ref_t is None and out_dtype == torch.float32) \
         else 0
@@ -107,10 +113,13 @@ def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype):
         assert y.stride(1) == 1 and y.dtype == w_post.dtype
     if add is not None:
         assert add.dtype == torch.float32 and add.is_contiguous()
-    check(_L().gllm_seq_resid_norm(_p(x), _p(y), y.stride(0) if y is not None else 0, _p(w_post), _p(add), _p(w_pre),
-                                   _p(out), t, width, float(eps), is32, stream_ptr()), "seq_resid_norm")
+    if y is None and add is None and w_pre is None and not plain:
+        return x if ret_x else None
+    check(_L().gllm_seq_resid_norm(_p(x), _p(y), y.stride(0) if y is not None else 0, _p(w_post), _p(post_scale),
+                                   _p(add), _p(w_pre), _p(out), t, width, float(eps), int(plain), is32, stream_ptr()),
+          "seq_resid_norm")
     sm100._count()
-    return out
+    return x if ret_x else out
 
 
 def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, k_cache, v_cache, slots):
@@ -171,13 +180,14 @@ def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc
     return out
 
 
-def causal_conv_silu(xz, channels, w, b, conv_state, rec_slots, seq_lens, query_start_loc):
+def causal_conv_silu(xz, channels, w, b, conv_state, rec_slots, seq_lens, query_start_loc, act="silu", in_bias=None):
     t = xz.shape[0]
     assert xz.stride(1) == 1 and w.dtype == torch.float32 and b.dtype == torch.float32
+    assert in_bias is None or (in_bias.dtype == torch.float32 and in_bias.is_contiguous())
     out = torch.empty(t, channels, dtype=xz.dtype, device=xz.device)
     check(_L().gllm_seq_conv_silu(_p(xz), xz.stride(0), t, seq_lens.shape[0], channels, _p(w), _p(b), w.shape[1],
                                   _p(conv_state), _p(rec_slots), _p(seq_lens), _p(query_start_loc), _p(out), _f32(xz),
-                                  stream_ptr()), "seq_conv_silu")
+                                  0 if act == "silu" else 1, _p(in_bias), stream_ptr()), "seq_conv_silu")
     sm100._count(2 if conv_state is not None else 1)
     return out
 
@@ -233,12 +243,13 @@ def qk_norm_rope_kv_write(qkv, num_heads, num_kv_heads, dim, v_dim, q_norm_w, k_
 
 
 def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, rec_slots, seq_lens, query_start_loc, heads,
-                      qk_heads, dim, v_dim, silu_in, unit_qk, q_scale, delta):
+                      qk_heads, dim, v_dim, silu_in, unit_qk, q_scale, delta, zk=None, zk_bias=None, inv_tau=1.0):
     t = q.shape[0]
-    for x in (q, k, v, beta, a):
+    for x in (q, k, v, beta, a, zk):
         assert x is None or (x.stride(1) == 1 and x.dtype == q.dtype)
     assert state is None or (state.dtype == torch.float32 and state.is_contiguous())
-    assert (decay is None) != (a is None) and (not delta or beta is not None)
+    assert (decay is not None) + (a is not None) + (zk is not None) == 1 and (not delta or beta is not None)
+    assert zk_bias is None or (zk_bias.dtype == torch.float32 and zk_bias.is_contiguous())
     out = torch.empty(t, heads * v_dim, dtype=torch.float32, device=q.device)
     ld = lambda x: x.stride(0) if x is not None else 0   # noqa: E731
     # long chunks on a grid that leaves SMs idle: 8 lanes per state column (twice the warps on the serial chain;
@@ -251,7 +262,8 @@ def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, rec_slots,
                                      _p(a), ld(a), _p(neg_a), _p(dt_bias), _p(decay), _p(state), _p(rec_slots),
                                      _p(seq_lens), _p(query_start_loc), seq_lens.shape[0], heads, qk_heads, dim, v_dim,
                                      int(silu_in), int(unit_qk), float(q_scale), int(delta), _p(out), _f32(q),
-                                     parts, stream_ptr()), "seq_linear_state")
+                                     parts, _p(zk), ld(zk), _p(zk_bias), float(inv_tau), stream_ptr()),
+          "seq_linear_state")
     sm100._count()
     return out
 
@@ -282,15 +294,12 @@ _ROUTER_MMA_MIN_TOKENS = 256
 _NUM_SMS = 148
 
 
-def router_topk(h, w, top_k, force: Optional[str] = None):
-    """fp32 router logits h . w^T, then the top_k largest per token and the softmax over the chosen (one warp per
-    token). Logits: small batches, one warp per (token, expert); large bf16 batches on the tensor cores (mma.sync,
-    fp32 accumulation and fp32 result); large fp32 batches, the plain GEMM with fp32 result."""
+def router_logits(h, w, force: Optional[str] = None):
+    """fp32 router logits h . w^T [T, E]. Small batches: one warp per (token, expert); large bf16 batches on the
+    tensor cores (mma.sync, fp32 accumulation and fp32 result); large fp32 batches: the plain GEMM with fp32 result."""
     t, width = h.shape
     e = w.shape[0]
-    assert h.stride(1) == 1 and w.is_contiguous() and h.dtype == w.dtype and e <= 1024
-    wout = torch.empty(t, top_k, dtype=torch.float32, device=h.device)
-    ids = torch.empty(t, top_k, dtype=torch.int32, device=h.device)
+    assert h.stride(1) == 1 and w.is_contiguous() and h.dtype == w.dtype
     logits = torch.empty(t, e, dtype=torch.float32, device=h.device)
     L, st = _L(), stream_ptr()
     mma_ok = h.dtype == torch.bfloat16 and width % 16 == 0 and h.stride(0) % 2 == 0 and h.data_ptr() % 4 == 0
@@ -304,19 +313,35 @@ def router_topk(h, w, top_k, force: Optional[str] = None):
     else:
         check(L.gllm_seq_gemm_simt_f32out(_p(h), h.stride(0), _p(w), w.stride(0), _p(logits), e, t, e, width, _f32(h),
                                           st), "seq_gemm_simt_f32out")
+    sm100._count()
+    return logits
+
+
+def router_topk(h, w, top_k, force: Optional[str] = None):
+    """fp32 router logits (`router_logits`), then the top_k largest per token and the softmax over the chosen (one
+    warp per token)."""
+    t, e = h.shape[0], w.shape[0]
+    assert e <= 1024
+    wout = torch.empty(t, top_k, dtype=torch.float32, device=h.device)
+    ids = torch.empty(t, top_k, dtype=torch.int32, device=h.device)
+    logits = router_logits(h, w, force)
+    L, st = _L(), stream_ptr()
     check(L.gllm_seq_router_select(_p(logits), t, e, top_k, _p(wout), _p(ids), st), "seq_router_select")
-    sm100._count(2)
+    sm100._count()
     return wout, ids
 
 
-def routed_experts(h, w13, w2, weights, ids):
+def routed_experts(h, w13, w2, weights, ids, limit: float = 0.0, alpha: float = 1.702, n_real: Optional[int] = None):
+    """Plain per-slot experts. limit > 0: the clamped gated activation; ids >= n_real: identity experts."""
     t, width = h.shape
+    n_real = w13.shape[0] if n_real is None else n_real
     f, k = w13.shape[1] // 2, ids.shape[1]
     assert h.stride(1) == 1 and w13.is_contiguous() and w2.is_contiguous() and weights.is_contiguous()
     act = torch.empty(t * k, f, dtype=h.dtype, device=h.device)
     out = torch.empty(t, width, dtype=h.dtype, device=h.device)
     check(_L().gllm_seq_routed_experts(_p(h), h.stride(0), _p(w13), _p(w2), _p(ids), _p(weights), t, k, width, f,
-                                       _p(act), _p(out), _f32(h), stream_ptr()), "seq_routed_experts")
+                                       _p(act), _p(out), _f32(h), int(n_real), float(limit), float(alpha),
+                                       stream_ptr()), "seq_routed_experts")
     sm100._count(2)
     return out
 
