@@ -1,10 +1,12 @@
 """Prefill / decode throughput of a layer-list design beside the closest existing decoder at matched width, depth and
 (roughly) parameter count, through the public `LLM.generate` API with random weights, plus the device time of each
 new kernel against its roofline and against the like kernel of the existing path. Invoked as
-`python bench.py --design saritar|femolix` (the default benchmark is untouched).
+`python bench.py --design saritar|femolix|bevovik` (the default benchmark is untouched).
 
   saritar  beside Qwen3 (GQA attention with q/k norm + gated MLP)
   femolix  beside Qwen3-MoE (rotary GQA attention with q/k norm + routed gated experts)
+  bevovik  beside DeepSeek-V3 (latent attention with YaRN rotary + group-limited routing with a correction bias and a
+           shared expert)
 
 Prints ONE JSON line: {"design": ..., "sizes": [{"width", ..., "<design>": {...}, "<closest>": {...}}], "kernels": [...]}
 """
@@ -60,6 +62,40 @@ def _qwen3_moe_cfg(width, layers, vocab, experts=16, top=2):
             "intermediate_size": 3 * width, "moe_intermediate_size": width, "num_experts": experts,
             "num_experts_per_tok": top, "norm_topk_prob": True, "decoder_sparse_step": 1, "mlp_only_layers": [0],
             "vocab_size": vocab, "rms_norm_eps": 1e-6, "rope_theta": 1e6, "max_position_embeddings": 8192,
+            "tie_word_embeddings": False, "torch_dtype": "bfloat16"}
+
+
+def _bevovik_cfg(width, n_quads, vocab, experts=14, identity=2, top=2):
+    """[recurrent unit, key-decay linear attention, latent attention, recurrent unit] x n_quads, every layer with a
+    routed feed-forward (experts + identity outputs in 4 groups of which 2 are kept) and a shared expert."""
+    heads = width // 128
+    ff = {"kind": "moe", "expert": {"ff": width // 2, "limit": 7.0},
+          "router": {"experts": experts, "identity": identity, "top": top, "scale": 2.5,
+                     "groups": {"count": 4, "keep": 2}},
+          "shared": {"ff": width, "limit": 7.0}}
+    rg = {"type": "rglru", "mixer": {"width": width, "blocks": width // 128, "conv": 4}, "mlp": ff}
+    gl = {"type": "gla", "mixer": {"heads": heads // 2, "dim": 128, "vdim": 256, "tau": 16.0}, "mlp": ff}
+    la = {"type": "latent_attention",
+          "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": max(width // 4, 384),
+                    "kv_rank": 512, "scale": 192 ** -0.5,
+                    "rot": {"base": 10000.0, "dims": 64,
+                            "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}, "mlp": ff}
+    return {"architecture": "Bevovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [rg, gl, la, rg] * n_quads}
+
+
+def _deepseek_cfg(width, layers, vocab, experts=16, top=2):
+    heads = width // 128
+    return {"architectures": ["DeepseekV3ForCausalLM"], "hidden_size": width, "num_hidden_layers": layers,
+            "num_attention_heads": heads, "num_key_value_heads": heads, "intermediate_size": 3 * width,
+            "moe_intermediate_size": width // 2, "n_routed_experts": experts, "n_shared_experts": 2,
+            "num_experts_per_tok": top, "n_group": 4, "topk_group": 2, "topk_method": "noaux_tc",
+            "scoring_func": "sigmoid", "norm_topk_prob": True, "routed_scaling_factor": 2.5,
+            "first_k_dense_replace": 0, "moe_layer_freq": 1, "q_lora_rank": max(width // 4, 384),
+            "kv_lora_rank": 512, "qk_nope_head_dim": 128, "qk_rope_head_dim": 64, "v_head_dim": 128,
+            "vocab_size": vocab, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 8192,
+            "rope_scaling": {"type": "yarn", "factor": 8, "original_max_position_embeddings": 1024, "beta_fast": 32,
+                             "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0},
             "tie_word_embeddings": False, "torch_dtype": "bfloat16"}
 
 
@@ -320,6 +356,8 @@ def run(args):
             peaks = json.load(f)
     if getattr(args, "design", "saritar") == "femolix":
         return run_femolix(args, peaks)
+    if getattr(args, "design", "saritar") == "bevovik":
+        return run_bevovik(args, peaks)
     vocab = 32000
     kernels = _kernels(peaks)
     sizes = []
@@ -330,6 +368,185 @@ def run(args):
                       "saritar": _throughput(s_cfg, vocab, args.warmup, args.steps),
                       "qwen3": _throughput(q_cfg, vocab, args.warmup, args.steps)})
     line = {"design": "saritar", "dtype": "bf16", "data": "synthetic", "warmup": args.warmup, "steps": args.steps,
+            "timing": "wall clock around LLM.generate with synchronize (sizes); CUDA events, L2 flushed (kernels)",
+            "peaks": peaks, "sizes": sizes, "kernels": kernels}
+    print(json.dumps(line))
+    return line
+
+
+def _kernels_bevovik(peaks):
+    """Device time of the kernels this design added or extended, at layer-like sizes, each beside the like kernel
+    of the existing path (DeepSeek's latent attention and routing; the recurrent kernels of the other layer-list
+    designs). Bytes are the algorithmic minimum."""
+    from gllm_b200.ops import ref, sm100, sm100_latent as Lt, sm100_moe, sm100_seq as S
+    dev, bf = "cuda", torch.bfloat16
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    out = []
+
+    def row(name, ms, nbytes, like=None, flops=None):
+        r = {"kernel": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+             "frac_hbm": round(nbytes / ms / 1e6 / hbm, 3)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+        if like:
+            r["like"] = like
+        out.append(r)
+
+    T, W = 8192, 4096
+    x = torch.randn(T, W, device=dev)
+    y, w1, ls = torch.randn(T, W, device=dev).to(bf), torch.ones(W, device=dev).to(bf), torch.rand(W, device=dev)
+    row("resid_norm (branch norm * layer scale + add, fp32 stream in/out, bf16 in/out)",
+        _time(lambda: S.resid_norm(x, y, w1, None, None, 1e-5, bf, True, ls)), T * W * (4 + 4 + 2 + 2))
+    res = torch.randn(T, W, device=dev).to(bf)
+    row("rmsnorm + residual (existing bf16 path)", _time(lambda: sm100.rmsnorm(y, w1, 1e-5, res)),
+        T * W * (2 + 2 + 2 + 2), like="resid_norm")
+
+    # real-gated recurrent unit: convolution, block-diagonal gates, scan
+    C, NB = 4096, 32
+    bw = C // NB
+    for label, qlens in (("prefill 4 x 2048", [2048] * 4), ("decode 256 x 1", [1] * 256)):
+        Tt, B = sum(qlens), len(qlens)
+        qsl = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+        sl = torch.tensor([q + 100 for q in qlens], dtype=torch.int32, device=dev)
+        rs = torch.arange(B, dtype=torch.int32, device=dev)
+        proj = torch.randn(Tt, 2 * C, device=dev).to(bf)
+        cw, cb, xb = torch.randn(C, 4, device=dev), torch.randn(C, device=dev), torch.randn(C, device=dev)
+        cs = torch.zeros(B, 3, C, device=dev).to(bf)
+        row("conv (no activation, input bias) " + label,
+            _time(lambda: S.causal_conv_silu(proj[:, C:], C, cw, cb, cs, rs, sl, qsl, "none", xb)),
+            Tt * C * 4 + B * 3 * C * 4)
+        row("conv_silu (existing) " + label,
+            _time(lambda: S.causal_conv_silu(proj[:, C:], C, cw, cb, cs, rs, sl, qsl)), Tt * C * 4 + B * 3 * C * 4,
+            like="conv")
+        u = S.causal_conv_silu(proj[:, C:], C, cw, cb, cs, rs, sl, qsl, "none", xb)
+        gw = (torch.randn(NB, 2 * bw, bw, device=dev) * bw ** -0.5).to(bf)
+        fl = 2.0 * Tt * NB * 2 * bw * bw
+        row("block_linear gates (block-diagonal, fp32 result) " + label,
+            _time(lambda: Lt.block_linear(u, gw, torch.float32)), Tt * C * 2 + Tt * 2 * C * 4 + gw.numel() * 2,
+            flops=fl)
+        row("block_linear (tcgen05 batched GEMM, bf16 result) " + label, _time(lambda: Lt.block_linear(u, gw)),
+            Tt * C * 2 + Tt * 2 * C * 2 + gw.numel() * 2, like="block_linear gates", flops=fl)
+        gates = Lt.block_linear(u, gw, torch.float32)
+        gb, cd, yb = torch.randn(2 * C, device=dev), -8.0 * torch.rand(C, device=dev), torch.randn(C, device=dev)
+        st = torch.zeros(B, 1, C, device=dev)
+        row("rglru_scan (gates + decay + recurrence + output gate) " + label,
+            _time(lambda: Lt.rglru_scan(u, gates, gb, cd, proj, yb, st, rs, sl, qsl, bw, bf, max_q_len=max(qlens)),
+                  iters=5), Tt * C * (2 + 8 + 2 + 2) + B * C * 8)
+        if qlens[0] > 1:
+            N, R = 16, 256
+            pj, dtr = torch.randn(Tt, R + 2 * N, device=dev).to(bf), torch.randn(Tt, C, device=dev).to(bf)
+            A, Dk, db2 = -torch.rand(C, N, device=dev), torch.randn(C, device=dev), torch.randn(C, device=dev)
+            ss = torch.zeros(B, N, C, device=dev)
+            row("selective_scan (existing recurrent kernel, 16 states per channel) " + label,
+                _time(lambda: S.selective_scan(u, dtr, pj, proj, A, Dk, db2, ss, rs, sl, qsl, C, N, R), iters=5),
+                Tt * C * 2 * 4 + B * N * C * 8, like="rglru_scan")
+
+    # key-decay gated linear attention
+    Hh, Dd, V, Rk = 16, 128, 256, 16
+    for label, qlens in (("prefill 4 x 2048", [2048] * 4), ("decode 256 x 1", [1] * 256)):
+        Tt, B = sum(qlens), len(qlens)
+        qsl = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+        sl = torch.tensor([q + 100 for q in qlens], dtype=torch.int32, device=dev)
+        rs = torch.arange(B, dtype=torch.int32, device=dev)
+        qk = torch.randn(Tt, 2 * Hh * Dd, device=dev).to(bf)
+        v = torch.randn(Tt, Hh * V, device=dev).to(bf)
+        zk, zb = torch.randn(Tt, Hh * Dd, device=dev).to(bf), torch.randn(Hh * Dd, device=dev) + 3.0
+        st = torch.zeros(B, Hh, Dd, V, device=dev)
+        nbytes = Tt * (3 * Hh * Dd + Hh * V) * 2 + Tt * Hh * V * 4 + B * Hh * Dd * V * 8
+        row("linear_state_scan (decay per key channel) " + label,
+            _time(lambda: S.linear_state_scan(qk[:, :Hh * Dd], qk[:, Hh * Dd:], v, None, None, None, None, None, st, rs,
+                                              sl, qsl, Hh, Hh, Dd, V, False, False, Dd ** -0.5, False, zk=zk,
+                                              zk_bias=zb, inv_tau=1.0 / 16), iters=5),
+            nbytes, flops=5.0 * Tt * Hh * Dd * V)
+        dec = torch.full((Hh,), 0.99, device=dev)
+        row("linear_state_scan (existing: one constant decay per head) " + label,
+            _time(lambda: S.linear_state_scan(qk[:, :Hh * Dd], qk[:, Hh * Dd:], v, None, None, None, None, dec, st, rs,
+                                              sl, qsl, Hh, Hh, Dd, V, True, False, 1.0, False), iters=5),
+            nbytes - Tt * Hh * Dd * 2, like="linear_state_scan (decay per key channel)",
+            flops=4.0 * Tt * Hh * Dd * V)
+
+    # latent attention: norm + pair rotary + cache write, then the attention over the latent cache
+    H, Dn, rot, rank, ps = 32, 128, 64, 512, 16
+    for label, qlens, ctx in (("prefill 4 x 2048", [2048] * 4, 0), ("decode 256 x 1 at 2048", [1] * 256, 2047)):
+        Tt, B = sum(qlens), len(qlens)
+        npp = (max(qlens) + ctx + ps - 1) // ps
+        bt = torch.arange(B * npp, dtype=torch.int32, device=dev).reshape(B, npp)
+        cache = torch.randn(B * npp + 1, 1, (rank + rot) // 64, ps, 64, device=dev).to(bf)
+        pos = torch.cat([torch.arange(ctx, ctx + q) for q in qlens]).to(torch.int32).to(dev)
+        seqi = torch.cat([torch.full((q,), i) for i, q in enumerate(qlens)]).to(dev)
+        slots = (bt[seqi, (pos // ps).long()] * ps + pos % ps).to(torch.int32)
+        q = torch.randn(Tt, H, Dn + rot, device=dev).to(bf)
+        dkv = torch.randn(Tt, rank + rot, device=dev).to(bf)
+        q_full = torch.randn(Tt, H, rank + rot, device=dev).to(bf)
+        nw = torch.ones(rank, device=dev).to(bf)
+        fr, mag = ref.pair_rotary_frequencies(rot, 10000.0, {"factor": 8.0, "original": 1024, "fast": 32.0,
+                                                             "slow": 1.0})
+        fr = fr.to(dev)
+        nb = Tt * (H * rot * 2 * 2 + (rank + rot) * 2 * 2)
+        row("latent_norm_rope_write (latent norm + pair rotary from fp32 angles + cache write) " + label,
+            _time(lambda: Lt.latent_norm_rope_write(q, dkv, rank, rot, nw, 1e-5, pos, fr, mag, q_full, cache, slots)),
+            nb)
+        cs = torch.randn(8192, rot, device=dev)
+        kvn = torch.randn(Tt, rank, device=dev).to(bf)
+        row("rmsnorm(latent) + mla_rope_cache (existing: table rotary + cache write) " + label,
+            _time(lambda: (sm100.rmsnorm(dkv[:, :rank], nw, 1e-5),
+                           sm100.mla_rope_cache(q[:, :, Dn:], q_full, dkv[:, rank:], kvn, cs, pos, slots, cache))),
+            nb + Tt * rank * 2 * 2, like="latent_norm_rope_write")
+        tok_seq = seqi.to(torch.int32)
+        keys = sum(p + 1 for ql in qlens for p in range(ctx, ctx + ql))
+        ms = _time(lambda: sm100.mla_attention(q_full, cache, bt, tok_seq, pos, 192 ** -0.5), iters=3)
+        out.append({"kernel": "latent attention 512 + 64 (the DeepSeek tensor-core kernel itself) " + label,
+                    "ms": round(ms, 4), "tflops": round(2.0 * keys * H * (2 * rank + rot) / ms / 1e9, 2)})
+
+    # router and experts
+    T2, E, top = 8192, 16, 2
+    hh = torch.randn(T2, W, device=dev).to(bf)
+    wr, corr = (torch.randn(E, W, device=dev) * W ** -0.5).to(bf), torch.randn(E, device=dev) * 0.1
+    row("grouped_router (fp32 logits + softmax + correction + group limit + top-2) 8192 x 4096 x 16",
+        _time(lambda: Lt.grouped_router(hh, wr, corr, top, 4, 2, 2.5)), T2 * W * 2 + E * W * 2)
+    row("router GEMM + grouped_topk (existing)",
+        _time(lambda: sm100_moe.grouped_topk(sm100.linear(hh, wr), top, True, 4, 2, "sigmoid", corr, 2.5)),
+        T2 * W * 2 + E * W * 2, like="grouped_router")
+    hd = hh[:64]
+    row("grouped_router decode, 64 x 4096 x 16", _time(lambda: Lt.grouped_router(hd, wr, corr, top, 4, 2, 2.5)),
+        E * W * 2 + 64 * W * 2)
+    row("router GEMM + grouped_topk decode (existing)",
+        _time(lambda: sm100_moe.grouped_topk(sm100.linear(hd, wr), top, True, 4, 2, "sigmoid", corr, 2.5)),
+        E * W * 2 + 64 * W * 2, like="grouped_router decode")
+    F = 2048
+    n_real = E - 2
+    w13 = (torch.randn(n_real, 2 * F, W, device=dev) * W ** -0.5).to(bf)
+    w2 = (torch.randn(n_real, W, F, device=dev) * F ** -0.5).to(bf)
+    wts, ids = Lt.grouped_router(hh, wr, corr, top, 4, 2, 2.5)
+    fl = 6.0 * T2 * top * W * F * n_real / E
+    row("routed_glu_experts (grouped tcgen05 GEMMs, clamped gated epilogue, 2 identity experts of 16)",
+        _time(lambda: Lt.routed_glu_experts(hh, w13, w2, wts, ids, 7.0, True, 1.702, E), iters=5),
+        w13.numel() * 2 + w2.numel() * 2 + T2 * W * 2 * 2, flops=fl)
+    ids2 = ids % n_real
+    row("fused_experts (existing: SiLU-gate epilogue, 14 experts)",
+        _time(lambda: sm100_moe.fused_experts(hh, w13, w2, wts, ids2), iters=5),
+        w13.numel() * 2 + w2.numel() * 2 + T2 * W * 2 * 2, like="routed_glu_experts", flops=6.0 * T2 * top * W * F)
+    Fs = 4096
+    wgu = (torch.randn(2 * Fs, W, device=dev) * W ** -0.5).to(bf)
+    row("linear_glu_clamp (tcgen05 GEMM, clamped gated epilogue) 8192 x 4096 -> 4096",
+        _time(lambda: Lt.linear_glu_clamp(hh, wgu, 7.0), iters=5), wgu.numel() * 2 + T2 * (W + Fs) * 2,
+        flops=4.0 * T2 * W * Fs)
+    row("linear_silu_mul (existing epilogue)", _time(lambda: sm100.linear_silu_mul(hh, wgu), iters=5),
+        wgu.numel() * 2 + T2 * (W + Fs) * 2, like="linear_glu_clamp", flops=4.0 * T2 * W * Fs)
+    return out
+
+
+def run_bevovik(args, peaks):
+    vocab = 32000
+    kernels = _kernels_bevovik(peaks)
+    sizes = []
+    for width, quads in ((1024, 2), (2048, 2), (4096, 1)):
+        b_cfg = _bevovik_cfg(width, quads, vocab)
+        d_cfg = _deepseek_cfg(width, 4 * quads, vocab)
+        sizes.append({"width": width, "layers": 4 * quads,
+                      "bevovik": _throughput(b_cfg, vocab, args.warmup, args.steps),
+                      "deepseek_v3": _throughput(d_cfg, vocab, args.warmup, args.steps)})
+    line = {"design": "bevovik", "dtype": "bf16", "data": "synthetic", "warmup": args.warmup, "steps": args.steps,
             "timing": "wall clock around LLM.generate with synchronize (sizes); CUDA events, L2 flushed (kernels)",
             "peaks": peaks, "sizes": sizes, "kernels": kernels}
     print(json.dumps(line))

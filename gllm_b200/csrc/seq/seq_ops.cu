@@ -178,8 +178,9 @@ __global__ void __launch_bounds__(128) window_attn_kernel(
 }
 
 // depthwise causal convolution + SiLU (act 0) or no activation (act 1); taps before the chunk come from the
-// sequence's carried state. in_bias (optional) is added to every input at a position >= 0; the zeros before the
-// start of a sequence stay zeros, and the carried state holds the inputs without it.
+// sequence's carried state. in_bias (optional) is added to every input at a position >= 0; inputs before the
+// start of a sequence are zeros (the slot's rows for them are not read), and the carried state holds the inputs
+// without the bias.
 template <typename T>
 __global__ void conv_silu_kernel(const T* __restrict__ xz, long ldxz, int C, const float* __restrict__ w,
                                  const float* __restrict__ b, int taps, const T* __restrict__ state,
@@ -202,7 +203,7 @@ __global__ void conv_silu_kernel(const T* __restrict__ xz, long ldxz, int C, con
     float v = 0.f;
     if (src >= 0) v = to_f(xz[(size_t)(q0 + src) * ldxz + c]);
     else if (carried) v = to_f(st[(size_t)(taps - 1 + src) * C + c]);
-    if (pos0 + src >= 0) v += ib;
+    v = pos0 + src >= 0 ? v + ib : 0.f;        // nothing precedes position 0, whatever the slot held
     acc = fmaf(w[(size_t)c * taps + j], v, acc);
   }
   out[(size_t)t * C + c] = from_f<T>(act == 0 ? acc / (1.0f + expf(-acc)) : acc);

@@ -100,7 +100,8 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_write_kernel(
 // costs two register passes and two PARTS-lane shuffle reductions (PARTS = 8 for head sizes >= 128: half the
 // registers per thread, twice the warps in flight). q / k rows and the per-token g, beta of TCH tokens are staged
 // in shared memory by the whole block (SiLU, unit length and the q scale applied there). With KD the decay is one
-// value per key channel, g[d] = sigmoid(zk[d] + zk_bias[d])^inv_tau (a third staged row per token), acting on row d.
+// value per key channel, gk[t, h * D + d] in fp32 (`key_decay_kernel`), acting on row d; it is staged beside the key as
+// (k, decay) pairs, so the update still costs two shared loads per state entry.
 template <typename T, int NS, int PARTS, bool KD>
 __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
     const T* __restrict__ q, long ldq, const T* __restrict__ k, long ldk, const T* __restrict__ v, long ldv,
@@ -108,12 +109,15 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
     const float* __restrict__ dt_bias, const float* __restrict__ decay, float* __restrict__ state,
     const int* __restrict__ rec_slots, const int* __restrict__ seq_lens, const int* __restrict__ qsl, int H, int G,
     int D, int V, int silu_in, int unit_qk, float q_scale, int delta, float* __restrict__ out,
-    const T* __restrict__ zk, long ldz, const float* __restrict__ zk_bias, float inv_tau) {
+    const float* __restrict__ gk, long ldgk) {
   constexpr int TCH = 8;               // tokens staged per round (16 measured 2.4x slower: registers)
   constexpr int ROWS = KD ? 3 : 2;
   extern __shared__ float sm[];
-  float* sq = sm;                      // [TCH][ROWS][D]: q row, k row (, decay row)
-  float* sg = sm + TCH * ROWS * D;     // [TCH][2]: g, beta
+  // per token TS floats: [q row | k row], or with KD [(k, decay) pairs | q row] on an even stride (8-byte loads)
+  const int TS = KD ? ((3 * D + 1) & ~1) : 2 * D;
+  const int qoff = KD ? 2 * D : 0, koff = KD ? 0 : D;
+  float* sq = sm;
+  float* sg = sm + TCH * TS;           // [TCH][2]: g, beta
   const int s = blockIdx.x, h = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int NT = 32 * PARTS, NW = PARTS;       // threads and warps per block
@@ -138,16 +142,15 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
     for (int idx = threadIdx.x; idx < nt * ROWS * D; idx += NT) {
       const int kk = idx / (ROWS * D), r = idx - kk * ROWS * D;
       float f;
+      const int dst = kk * TS + (!KD ? r : r < D ? qoff + r : r < 2 * D ? 2 * (r - D) : 2 * (r - 2 * D) + 1);
       if (KD && r >= 2 * D) {
-        const int c = h * D + r - 2 * D;
-        const float z = to_f(zk[(size_t)(t0 + kk) * ldz + c]) + (zk_bias != nullptr ? zk_bias[c] : 0.f);
-        f = expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * inv_tau);      // sigmoid(z)^inv_tau
+        f = gk[(size_t)(t0 + kk) * ldgk + h * D + r - 2 * D];
       } else {
         f = r < D ? to_f(q[(size_t)(t0 + kk) * ldq + (size_t)kvh * D + r])
                   : to_f(k[(size_t)(t0 + kk) * ldk + (size_t)kvh * D + r - D]);
         if (silu_in) f = silu_f(f);
       }
-      sq[idx] = f;
+      sq[dst] = f;
     }
     if (threadIdx.x < nt) {
       float g, b = 1.0f;
@@ -166,7 +169,8 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
     __syncthreads();
     if (unit_qk || q_scale != 1.0f) {
       for (int row = warp; row < 2 * nt; row += NW) {      // row = token * 2 + (0: q, 1: k)
-        float* ptr = sq + (size_t)((row >> 1) * ROWS + (row & 1)) * D;
+        if (KD && (row & 1)) continue;                       // keys are neither scaled nor normed with a key decay
+        float* ptr = sq + (size_t)(row >> 1) * TS + ((row & 1) ? koff : qoff);
         float sc = (row & 1) ? 1.0f : q_scale;
         if (unit_qk) {
           float ss = 0.f;
@@ -188,9 +192,9 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
 #pragma unroll
     for (int kk = 0; kk < TCH; ++kk) {
       if (kk < nt) {
-        const float* qq = sq + (size_t)kk * ROWS * D;
-        const float* kr = qq + D;
-        const float* gr = qq + (ROWS - 1) * D;          // the decay row with KD
+        const float* qq = sq + (size_t)kk * TS + qoff;
+        const float* kr = sq + (size_t)kk * TS + koff;
+        const float2* kg = reinterpret_cast<const float2*>(kr);      // with KD: (k, decay) pairs
         const float g = sg[kk * 2], b = sg[kk * 2 + 1];
         float u = vv[kk];
         if (delta) {
@@ -209,7 +213,12 @@ __global__ void __launch_bounds__(32 * PARTS) linear_state_kernel(
         for (int j = 0; j < NS; ++j) {
           const int d = part + PARTS * j;
           if (d < D) {
-            S[j] = fmaf(kr[d], u, (KD ? gr[d] : g) * S[j]);
+            if (KD) {
+              const float2 p = kg[d];
+              S[j] = fmaf(p.x, u, p.y * S[j]);
+            } else {
+              S[j] = fmaf(kr[d], u, g * S[j]);
+            }
             o = fmaf(S[j], qq[d], o);
           }
         }
@@ -323,6 +332,95 @@ __global__ void __launch_bounds__(128) router_logits_mma_kernel(const __nv_bfloa
       if (r < ntok && ee < E) logits[(size_t)r * E + ee] = acc[n][c];
     }
   }
+}
+
+// Batched product with an fp32 result on the tensor cores: C_b[M, N] = A_b[M, K] . W_b[N, K]^T (bf16 operands, exact
+// products, fp32 accumulation in a fixed order per row). One warp computes 16 rows x NT * 8 columns with mma.sync
+// m16n8k16. The contraction index may be permuted as long as both operands use the same permutation, so a lane
+// takes 8 CONSECUTIVE k of its row with one 16-byte load (k0 + 8 t4 ...): entries 0..3 feed one mma's two k slots of
+// that lane, entries 4..7 a second mma. K % 32 == 0; rows, batch strides and bases 16-byte aligned.
+// SPLIT (few columns, e.g. router logits: too few 16-row tiles to fill the machine): the block's four warps share one
+// 16-row tile, each over a quarter of K (K % 128 == 0), and warp 0 adds the partial sums in warp order.
+template <int NT, bool SPLIT>
+__global__ void __launch_bounds__(128) gemm_mma_f32out_kernel(const __nv_bfloat16* __restrict__ A, long lda, long sa,
+                                                              const __nv_bfloat16* __restrict__ W, long ldw, long sw,
+                                                              float* __restrict__ C, long ldc, long sc, int M, int N,
+                                                              int K) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, t4 = lane & 3;
+  __shared__ float part[SPLIT ? 3 * NT * 4 * 32 : 1];
+  const int row0 = SPLIT ? blockIdx.x * 16 : (blockIdx.x * 4 + warp) * 16;
+  const int n0 = blockIdx.y * NT * 8;
+  if (row0 >= M) return;
+  A += (size_t)blockIdx.z * sa;
+  W += (size_t)blockIdx.z * sw;
+  C += (size_t)blockIdx.z * sc;
+  const int ra = min(row0 + g, M - 1), rb = min(row0 + g + 8, M - 1);         // clamped rows are never stored
+  const __nv_bfloat16* pa = A + (size_t)ra * lda + 8 * t4;
+  const __nv_bfloat16* pb = A + (size_t)rb * lda + 8 * t4;
+  const __nv_bfloat16* pw[NT];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) pw[n] = W + (size_t)min(n0 + n * 8 + g, N - 1) * ldw + 8 * t4;
+  float acc[NT][4];
+#pragma unroll
+  for (int n = 0; n < NT; ++n) { acc[n][0] = acc[n][1] = acc[n][2] = acc[n][3] = 0.f; }
+  const int kbeg = SPLIT ? warp * (K / 4) : 0, kend = SPLIT ? kbeg + K / 4 : K;
+#pragma unroll 2
+  for (int k0 = kbeg; k0 < kend; k0 += 32) {
+    const uint4 lo = *reinterpret_cast<const uint4*>(pa + k0);
+    const uint4 hi = *reinterpret_cast<const uint4*>(pb + k0);
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+      const uint4 b = *reinterpret_cast<const uint4*>(pw[n] + k0);
+      asm volatile(
+          "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+          "{%0, %1, %2, %3};"
+          : "+f"(acc[n][0]), "+f"(acc[n][1]), "+f"(acc[n][2]), "+f"(acc[n][3])
+          : "r"(lo.x), "r"(hi.x), "r"(lo.y), "r"(hi.y), "r"(b.x), "r"(b.y));
+      asm volatile(
+          "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+          "{%0, %1, %2, %3};"
+          : "+f"(acc[n][0]), "+f"(acc[n][1]), "+f"(acc[n][2]), "+f"(acc[n][3])
+          : "r"(lo.z), "r"(hi.z), "r"(lo.w), "r"(hi.w), "r"(b.z), "r"(b.w));
+    }
+  }
+  if (SPLIT) {
+    if (warp > 0) {
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) part[(((warp - 1) * NT + n) * 4 + c) * 32 + lane] = acc[n][c];
+    }
+    __syncthreads();
+    if (warp > 0) return;
+    for (int w = 0; w < 3; ++w)
+#pragma unroll
+      for (int n = 0; n < NT; ++n)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc[n][c] += part[((w * NT + n) * 4 + c) * 32 + lane];
+  }
+#pragma unroll
+  for (int n = 0; n < NT; ++n) {
+    const int col = n0 + n * 8 + 2 * t4;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int r = row0 + g + (c >> 1) * 8, cc = col + (c & 1);
+      if (r < M && cc < N) C[(size_t)r * ldc + cc] = acc[n][c];
+    }
+  }
+}
+
+// Decay per key channel for the matrix-state recurrence: out[t, c] = sigmoid(z[t, c] + bias[c])^inv_tau in fp32, formed
+// as exp(-softplus(-z) * inv_tau) (no cancellation for decays near 1).
+template <typename T>
+__global__ void key_decay_kernel(const T* __restrict__ z, long ldz, const float* __restrict__ bias, float inv_tau,
+                                 float* __restrict__ out, int n, size_t total) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total) return;
+  const size_t t = i / n;
+  const int c = (int)(i - t * n);
+  const float v = to_f(z[t * ldz + c]) + (bias != nullptr ? bias[c] : 0.f);
+  out[i] = expf((fminf(v, 0.f) - log1pf(expf(-fabsf(v)))) * inv_tau);
 }
 
 // Router, second half: one warp per token over its fp32 logits [E] (the first half is the fp32-output GEMM): the
@@ -444,12 +542,11 @@ int state_dispatch(dim3 grid, size_t smem, cudaStream_t st, const void* q, long 
                    const void* v, long ldv, const void* beta, long ldb, const void* a, long lda, const float* neg_a,
                    const float* dt_bias, const float* decay, float* state, const int* rec_slots, const int* seq_lens,
                    const int* qsl, int H, int G, int D, int V, int silu_in, int unit_qk, float q_scale, int delta,
-                   float* out, int parts, const void* zk, long ldz, const float* zk_bias, float inv_tau) {
+                   float* out, int parts, const float* zk, long ldz) {
 #define GLLM_STATE_KD(NS, PARTS, KD)                                                                                \
   linear_state_kernel<T, NS, PARTS, KD><<<grid, 32 * PARTS, smem, st>>>(                                            \
       (const T*)q, ldq, (const T*)k, ldk, (const T*)v, ldv, (const T*)beta, ldb, (const T*)a, lda, neg_a, dt_bias,  \
-      decay, state, rec_slots, seq_lens, qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta, out, (const T*)zk, ldz, \
-      zk_bias, inv_tau)
+      decay, state, rec_slots, seq_lens, qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta, out, zk, ldz)
 #define GLLM_STATE(NS, PARTS)                                               \
   do {                                                                      \
     if (zk != nullptr) GLLM_STATE_KD(NS, PARTS, true);                      \
@@ -512,25 +609,24 @@ GLLM_EXPORT int gllm_seq_linear_state(const void* q, long ldq, const void* k, lo
                                       const void* dt_bias, const void* decay, void* state, const void* rec_slots,
                                       const void* seq_lens, const void* qsl, int nseq, int H, int G, int D, int V,
                                       int silu_in, int unit_qk, float q_scale, int delta, void* out, int is_f32,
-                                      int parts, const void* zk, long ldz, const void* zk_bias, float inv_tau,
-                                      void* stream) {
+                                      int parts, const void* gk, long ldgk, void* stream) {
   if (nseq <= 0) return 0;
-  if (zk != nullptr && (delta || G != H)) return 2;                    // key-channel decay: plain update, own keys
+  if (gk != nullptr && (delta || G != H)) return 2;                    // key-channel decay: plain update, own keys
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(nseq, H, (V + 31) / 32);
   // TCH rows of q and k (and the decay row) + TCH (g, beta)
-  const size_t smem = (size_t)(8 * (zk != nullptr ? 3 : 2) * D + 16) * sizeof(float);
+  const size_t smem = (size_t)(8 * (gk != nullptr ? ((3 * D + 1) & ~1) : 2 * D) + 16) * sizeof(float);
   int rc;
   if (is_f32)
     rc = state_dispatch<float>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
                                (const float*)dt_bias, (const float*)decay, (float*)state, (const int*)rec_slots,
                                (const int*)seq_lens, (const int*)qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta,
-                               (float*)out, parts, zk, ldz, (const float*)zk_bias, inv_tau);
+                               (float*)out, parts, (const float*)gk, ldgk);
   else
     rc = state_dispatch<bf16_t>(grid, smem, st, q, ldq, k, ldk, v, ldv, beta, ldb, a, lda, (const float*)neg_a,
                                 (const float*)dt_bias, (const float*)decay, (float*)state, (const int*)rec_slots,
                                 (const int*)seq_lens, (const int*)qsl, H, G, D, V, silu_in, unit_qk, q_scale, delta,
-                                (float*)out, parts, zk, ldz, (const float*)zk_bias, inv_tau);
+                                (float*)out, parts, (const float*)gk, ldgk);
   if (rc) return rc;
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
@@ -589,6 +685,52 @@ GLLM_EXPORT int gllm_seq_router_logits_mma(const void* h, long ldh, const void* 
   dim3 grid((ntok + 63) / 64, (E + 63) / 64);
   router_logits_mma_kernel<8><<<grid, 128, 0, st>>>((const bf16_t*)h, ldh, (const bf16_t*)w, ntok, width, E,
                                                     (float*)logits);
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_gemm_mma_f32out(const void* A, long lda, long sa, const void* W, long ldw, long sw, void* C,
+                                         long ldc, long sc, int M, int N, int K, int B, void* stream) {
+  if (M <= 0 || N <= 0 || B <= 0) return 0;
+  if (K % 32 != 0 || lda % 8 != 0 || ldw % 8 != 0 || sa % 8 != 0 || sw % 8 != 0 || ((uintptr_t)A & 15) != 0 ||
+      ((uintptr_t)W & 15) != 0)
+    return 2;
+  cudaStream_t st = (cudaStream_t)stream;
+  const bf16_t* a = (const bf16_t*)A;
+  const bf16_t* w = (const bf16_t*)W;
+  // the choice depends on the shape only, never on the number of rows: one summation order per (N, K)
+  const bool split = N <= 32 && K % 128 == 0 && K >= 512;
+  if (split && N <= 16) {
+    dim3 grid((M + 15) / 16, 1, B);
+    gemm_mma_f32out_kernel<2, true><<<grid, 128, 0, st>>>(a, lda, sa, w, ldw, sw, (float*)C, ldc, sc, M, N, K);
+  } else if (split) {
+    dim3 grid((M + 15) / 16, 1, B);
+    gemm_mma_f32out_kernel<4, true><<<grid, 128, 0, st>>>(a, lda, sa, w, ldw, sw, (float*)C, ldc, sc, M, N, K);
+  } else if (N <= 16) {
+    dim3 grid((M + 63) / 64, 1, B);
+    gemm_mma_f32out_kernel<2, false><<<grid, 128, 0, st>>>(a, lda, sa, w, ldw, sw, (float*)C, ldc, sc, M, N, K);
+  } else if (N <= 32) {
+    dim3 grid((M + 63) / 64, 1, B);
+    gemm_mma_f32out_kernel<4, false><<<grid, 128, 0, st>>>(a, lda, sa, w, ldw, sw, (float*)C, ldc, sc, M, N, K);
+  } else {
+    dim3 grid((M + 63) / 64, (N + 63) / 64, B);
+    gemm_mma_f32out_kernel<8, false><<<grid, 128, 0, st>>>(a, lda, sa, w, ldw, sw, (float*)C, ldc, sc, M, N, K);
+  }
+  CUDA_CHECK_RET(cudaGetLastError());
+  return 0;
+}
+
+GLLM_EXPORT int gllm_seq_key_decay(const void* z, long ldz, const void* bias, float inv_tau, void* out, int ntok, int n,
+                                   int is_f32, void* stream) {
+  if (ntok <= 0 || n <= 0) return 0;
+  cudaStream_t st = (cudaStream_t)stream;
+  const size_t total = (size_t)ntok * n;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  GLLM_BY_DTYPE(is_f32,
+                (key_decay_kernel<bf16_t><<<blocks, 256, 0, st>>>((const bf16_t*)z, ldz, (const float*)bias, inv_tau,
+                                                                  (float*)out, n, total)),
+                (key_decay_kernel<float><<<blocks, 256, 0, st>>>((const float*)z, ldz, (const float*)bias, inv_tau,
+                                                                 (float*)out, n, total)));
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }

@@ -577,10 +577,8 @@ def causal_conv_silu(xz: torch.Tensor, channels: int, w: torch.Tensor, b: torch.
         if conv_state is not None and sl[s] - n > 0:
             hist = conv_state[int(rec_slots[s])][: taps - 1].float()
         xp = torch.cat([hist, x], 0)
-        xin = xp
-        if in_bias is not None:
-            xin = xp + in_bias.float()
-            xin[: taps - 1 - max(have, 0)] = 0.0
+        xin = xp + in_bias.float() if in_bias is not None else xp.clone()
+        xin[: taps - 1 - max(have, 0)] = 0.0         # nothing precedes position 0, whatever the slot held
         acc = b.float().expand(n, channels).clone()
         for j in range(taps):
             acc = acc + xin[j:j + n] * w[:, j].float()

@@ -107,6 +107,11 @@ def block_linear(x, w, out_dtype=None):
             sm100.gemm_batched(a3, w, o3)
             return out
     assert odt in (x.dtype, torch.float32)
+    if odt == torch.float32 and x.dtype == _BF16:
+        a3 = x.view(t, nb, k) if x.is_contiguous() else x.unflatten(1, (nb, k))
+        if sm100_seq.mma_f32out_ok(a3, w):       # whatever the batch size: one rounding behaviour per shape
+            sm100_seq.gemm_mma_f32out(a3, w, out.view(t, nb, n))
+            return out
     return _gemm_batched_plain(x, x.stride(0), k, w, k, n * k, out, nb * n, n, t, n, k, nb)
 
 

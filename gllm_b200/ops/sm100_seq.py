@@ -33,7 +33,9 @@ def _L():
             "gllm_seq_qk_norm_rope_kv_write": [P, G, I, I, I, I, I, P, P, F, P, I, ctypes.c_double, P, P, P, P, I, I, I,
                                                I, P],
             "gllm_seq_linear_state": [P, G, P, G, P, G, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P,
-                                      I, I, P, G, P, F, P],
+                                      I, I, P, G, P],
+            "gllm_seq_key_decay": [P, G, P, F, P, I, I, I, P],
+            "gllm_seq_gemm_mma_f32out": [P, G, G, P, G, G, P, G, G, I, I, I, I, P],
             "gllm_seq_gated_group_norm": [P, I, P, G, P, I, I, F, I, F, P, G, I, I, P],
             "gllm_seq_silu_mul": [P, G, I, I, P, I, P],
             "gllm_seq_router_select": [P, I, I, I, P, P, P],
@@ -252,6 +254,13 @@ def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, rec_slots,
     assert zk_bias is None or (zk_bias.dtype == torch.float32 and zk_bias.is_contiguous())
     out = torch.empty(t, heads * v_dim, dtype=torch.float32, device=q.device)
     ld = lambda x: x.stride(0) if x is not None else 0   # noqa: E731
+    gk = None
+    if zk is not None:
+        # the decays sigmoid(zk + bias)^inv_tau in fp32, once per (token, key channel) and off the serial chain
+        gk = torch.empty(t, heads * dim, dtype=torch.float32, device=q.device)
+        check(_L().gllm_seq_key_decay(_p(zk), zk.stride(0), _p(zk_bias), float(inv_tau), _p(gk), t, heads * dim,
+                                      _f32(zk), stream_ptr()), "seq_key_decay")
+        sm100._count()
     # long chunks on a grid that leaves SMs idle: 8 lanes per state column (twice the warps on the serial chain;
     # 4 x 2048 tokens, head size 128: 8 heads 1.9x faster, 32 heads 1.4x slower than 4 lanes). Otherwise 4: decode-like
     # batches want the wider contiguous runs of the state rows, whose read + write is all that a single token costs
@@ -262,8 +271,7 @@ def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, rec_slots,
                                      _p(a), ld(a), _p(neg_a), _p(dt_bias), _p(decay), _p(state), _p(rec_slots),
                                      _p(seq_lens), _p(query_start_loc), seq_lens.shape[0], heads, qk_heads, dim, v_dim,
                                      int(silu_in), int(unit_qk), float(q_scale), int(delta), _p(out), _f32(q),
-                                     parts, _p(zk), ld(zk), _p(zk_bias), float(inv_tau), stream_ptr()),
-          "seq_linear_state")
+                                     parts, _p(gk), ld(gk), stream_ptr()), "seq_linear_state")
     sm100._count()
     return out
 
@@ -303,6 +311,9 @@ def router_logits(h, w, force: Optional[str] = None):
     logits = torch.empty(t, e, dtype=torch.float32, device=h.device)
     L, st = _L(), stream_ptr()
     mma_ok = h.dtype == torch.bfloat16 and width % 16 == 0 and h.stride(0) % 2 == 0 and h.data_ptr() % 4 == 0
+    if force in (None, "mma") and h.dtype == torch.bfloat16 and (t >= _ROUTER_MMA_MIN_TOKENS or force == "mma") \
+            and mma_f32out_ok(h.unsqueeze(1), w.unsqueeze(0)):
+        return gemm_mma_f32out(h.unsqueeze(1), w.unsqueeze(0), logits.unsqueeze(1)).squeeze(1)
     path = force or ("token" if t < _ROUTER_MMA_MIN_TOKENS else ("mma" if mma_ok else "gemm"))
     if path == "token":
         check(L.gllm_seq_router_logits(_p(h), h.stride(0), _p(w), t, width, e, _p(logits), _f32(h), st),
@@ -315,6 +326,26 @@ def router_logits(h, w, force: Optional[str] = None):
                                           st), "seq_gemm_simt_f32out")
     sm100._count()
     return logits
+
+
+def mma_f32out_ok(a, w) -> bool:
+    """a [T, B, K] (strided), w [B, N, K] contiguous, both bf16: shapes the fp32-result tensor-core product takes."""
+    k = a.shape[2]
+    return a.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and k % 32 == 0 and a.stride(2) == 1 and \
+        a.stride(0) % 8 == 0 and (a.shape[1] == 1 or a.stride(1) % 8 == 0) and a.data_ptr() % 16 == 0 and \
+        w.is_contiguous() and w.data_ptr() % 16 == 0
+
+
+def gemm_mma_f32out(a, w, out):
+    """out[:, b, :] (fp32) = a[:, b, :] @ w[b].T with bf16 operands on mma.sync, fp32 accumulation and result."""
+    t, b, k = a.shape
+    n = w.shape[1]
+    assert out.dtype == torch.float32 and out.shape == (t, b, n) and out.stride(2) == 1 and mma_f32out_ok(a, w)
+    check(_L().gllm_seq_gemm_mma_f32out(_p(a), a.stride(0), a.stride(1) if b > 1 else 0, _p(w), k, n * k, _p(out),
+                                        out.stride(0), out.stride(1) if b > 1 else 0, t, n, k, b, stream_ptr()),
+          "seq_gemm_mma_f32out")
+    sm100._count()
+    return out
 
 
 def router_topk(h, w, top_k, force: Optional[str] = None):

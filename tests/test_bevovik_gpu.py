@@ -119,6 +119,37 @@ def test_batched_products_on_the_tensor_cores():
         assert close(o1, o2, 2e-2)
 
 
+def test_products_with_fp32_result_on_the_tensor_cores():
+    """bf16 operands, fp32 accumulation AND result: the block-diagonal gate product and the router logits on the
+    16-byte-load mma kernel (odd row counts, column counts off the tile, strided batch views), against fp32 matmul of
+    the same bf16 values; a row's result does not depend on the rows beside it."""
+    from gllm_b200.ops import sm100_latent as K, sm100_seq as S
+    torch.manual_seed(11)
+    dt = torch.bfloat16
+    for T in (1, 17, 300):
+        for nb, n, k in ((4, 128, 64), (3, 40, 32), (1, 264, 96)):
+            x = torch.randn(T, nb * k, device=DEV).to(dt)
+            w = (torch.randn(nb, n, k, device=DEV) / k ** 0.5).to(dt)
+            assert S.mma_f32out_ok(x.view(T, nb, k), w)
+            got = K.block_linear(x, w, torch.float32)
+            want = torch.einsum("tbk,bnk->tbn", x.float().view(T, nb, k), w.float()).reshape(T, nb * n)
+            assert got.dtype == torch.float32 and close(got, want, 1e-5), (T, nb, n, k)
+            if T > 1:
+                assert torch.equal(K.block_linear(x[T // 2:T // 2 + 1], w, torch.float32), got[T // 2:T // 2 + 1])
+        h = torch.randn(T, 5 * 64 + 8, device=DEV).to(dt)[:, 8:]          # rows 16-byte aligned, base offset 16 bytes
+        for e in (3, 10, 24, 70):
+            wr = (torch.randn(e, 5 * 64, device=DEV) / 16).to(dt)
+            got = S.router_logits(h, wr, force="mma")
+            assert close(got, h.float() @ wr.float().T, 1e-5), (T, e)
+        h2 = torch.randn(T, 640, device=DEV).to(dt)                       # wide and narrow: K split over the warps
+        for e in (5, 16, 30):
+            wr = (torch.randn(e, 640, device=DEV) / 25).to(dt)
+            got = S.router_logits(h2, wr, force="mma")
+            assert close(got, h2.float() @ wr.float().T, 1e-5), (T, e)
+            if T > 1:
+                assert torch.equal(S.router_logits(h2[T - 1:], wr, force="mma"), got[T - 1:])
+
+
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 3e-5), (torch.bfloat16, 2e-2)])
 def test_convolution_without_activation_and_input_bias(dt, tol):
     from gllm_b200.ops import ref, sm100_seq as S
@@ -195,7 +226,7 @@ def _latent_case(dt, heads, dim, rot, rank, qlens, ctx, ps, scale=0.3):
     tokens are already cached; -> (kernel result, unfused result)."""
     from gllm_b200.memory_manager import kv_cache_shape
     from gllm_b200.ops import ref, sm100_latent as K
-    pages = 2 + sum((c + q + ps - 1) // ps for c, q in zip(ctx, qlens)) * 2
+    pages = 2 + len(qlens) * max((c + q + ps - 1) // ps for c, q in zip(ctx, qlens))
     b = _batch(qlens, ctx, ps, pages)
     T = int(b.query_start_loc[-1])
     f, mag = ref.pair_rotary_frequencies(rot, 50000.0, {"factor": 8.0, "original": 64, "fast": 32.0, "slow": 1.0})
