@@ -79,7 +79,7 @@ def _bevovik_cfg(width, n_quads, vocab, experts=14, identity=2, top=2):
           "mixer": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "q_rank": max(width // 4, 384),
                     "kv_rank": 512, "scale": 192 ** -0.5,
                     "rot": {"base": 10000.0, "dims": 64,
-                            "scaling": {"factor": 8.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}, "mlp": ff}
+                            "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}, "mlp": ff}
     return {"architecture": "Bevovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "layers": [rg, gl, la, rg] * n_quads}
 
@@ -94,7 +94,7 @@ def _deepseek_cfg(width, layers, vocab, experts=16, top=2):
             "first_k_dense_replace": 0, "moe_layer_freq": 1, "q_lora_rank": max(width // 4, 384),
             "kv_lora_rank": 512, "qk_nope_head_dim": 128, "qk_rope_head_dim": 64, "v_head_dim": 128,
             "vocab_size": vocab, "rms_norm_eps": 1e-6, "rope_theta": 10000.0, "max_position_embeddings": 8192,
-            "rope_scaling": {"type": "yarn", "factor": 8, "original_max_position_embeddings": 1024, "beta_fast": 32,
+            "rope_scaling": {"type": "yarn", "factor": 4, "original_max_position_embeddings": 2048, "beta_fast": 32,
                              "beta_slow": 1, "mscale": 1.0, "mscale_all_dim": 1.0},
             "tie_word_embeddings": False, "torch_dtype": "bfloat16"}
 
@@ -479,7 +479,7 @@ def _kernels_bevovik(peaks):
         dkv = torch.randn(Tt, rank + rot, device=dev).to(bf)
         q_full = torch.randn(Tt, H, rank + rot, device=dev).to(bf)
         nw = torch.ones(rank, device=dev).to(bf)
-        fr, mag = ref.pair_rotary_frequencies(rot, 10000.0, {"factor": 8.0, "original": 1024, "fast": 32.0,
+        fr, mag = ref.pair_rotary_frequencies(rot, 10000.0, {"factor": 4.0, "original": 2048, "fast": 32.0,
                                                              "slow": 1.0})
         fr = fr.to(dev)
         nb = Tt * (H * rot * 2 * 2 + (rank + rot) * 2 * 2)

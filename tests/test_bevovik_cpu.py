@@ -106,7 +106,7 @@ def test_latent_attention_mixer_alone():
 def test_rotary_frequencies_and_rotation():
     """YaRN's ramp over the pair index, its clamps at both ends, no scaling, and the pair layout at far positions."""
     from gllm_b200.ops import ref
-    cases = [(16, 50000.0, None), (8, 100.0, U.YARN), (32, 10000.0, {"factor": 8.0, "original": 64, "fast": 32.0,
+    cases = [(16, 30000.0, None), (8, 100.0, U.YARN), (32, 10000.0, {"factor": 6.0, "original": 64, "fast": 24.0,
                                                                      "slow": 1.0}),
              (4, 10.0, {"factor": 2.0, "original": 4, "fast": 1000.0, "slow": 0.001}),      # ramp clamps to [0, 3]
              (6, 500.0, {"factor": 1.0, "original": 100, "fast": 4.0, "slow": 2.0}),

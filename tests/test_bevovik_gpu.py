@@ -229,7 +229,7 @@ def _latent_case(dt, heads, dim, rot, rank, qlens, ctx, ps, scale=0.3):
     pages = 2 + len(qlens) * max((c + q + ps - 1) // ps for c, q in zip(ctx, qlens))
     b = _batch(qlens, ctx, ps, pages)
     T = int(b.query_start_loc[-1])
-    f, mag = ref.pair_rotary_frequencies(rot, 50000.0, {"factor": 8.0, "original": 64, "fast": 32.0, "slow": 1.0})
+    f, mag = ref.pair_rotary_frequencies(rot, 30000.0, {"factor": 6.0, "original": 64, "fast": 24.0, "slow": 1.0})
     f = f.to(DEV)
     nw = (torch.rand(rank, device=DEV) + 0.5).to(dt)
     c1 = torch.zeros(kv_cache_shape(pages, 1, rank + rot, ps), dtype=dt, device=DEV)
