@@ -406,3 +406,22 @@ def test_greedy_generation_through_the_engine(models):
         for _ in range(n):
             cur.append(int(oracle.forward(cfg, w, cur, torch.float64)[-1].argmax()))
         assert s.token_ids == cur
+
+
+def test_side_benchmark_configuration_is_served():
+    """The layer-like configuration of `bench.py --design bevovik` (scaled down) is a valid model of this design:
+    it builds with random weights and generates through the engine."""
+    import os
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from benchmarks.design_bench import _bevovik_cfg
+    from gllm_b200.engine.llm_engine import LLM
+    cfg = _bevovik_cfg(256, 1, 97)
+    assert [L["type"] for L in cfg["layers"]] == ["rglru", "gla", "latent_attention", "rglru"]
+    r = cfg["layers"][0]["mlp"]["router"]
+    assert (r["experts"] + r["identity"]) % r["groups"]["count"] == 0
+    cfg["torch_dtype"] = "float32"
+    llm = LLM(cfg, load_format="dummy", page_size=4, maxp=16, maxd=4, num_cpu_pages=32, model_max_length=64,
+              log_stats=False, device="cpu", num_state_slots=2)
+    seqs = llm.generate(tokens=[toks(9, 97, 1), toks(4, 97, 2)], output_lens=[3, 2], temperature=0.0, top_k=1)
+    assert [len(s.token_ids) for s in seqs] == [12, 6]
