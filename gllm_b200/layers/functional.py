@@ -111,12 +111,13 @@ def _seq():
     return sm100_seq
 
 
-def linear_any(x, w):
-    """y = x @ w.T for bf16 or fp32 operands of any shape: the tcgen05 GEMM when it applies (bf16, 16-byte aligned
-    rows), else the plain fp32-accumulating kernel (true fp32 for fp32 operands, no TF32)."""
+def linear_any(x, w, bias=None):
+    """y = x @ w.T (+ bias, added to the fp32 accumulator) for bf16 or fp32 operands of any shape: the tcgen05 GEMM
+    when it applies (bf16, 16-byte aligned rows), else the plain fp32-accumulating kernel (true fp32 for fp32
+    operands, no TF32)."""
     if x.is_cuda:
-        return _seq().linear_any(x, w)
-    return ref.linear(x, w)
+        return _seq().linear_any(x, w, bias)
+    return ref.linear(x, w, bias)
 
 
 def embedding_scaled(ids, table, scale):
@@ -125,10 +126,10 @@ def embedding_scaled(ids, table, scale):
     return ref.embedding_scaled(ids, table, scale)
 
 
-def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None):
+def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None, w_offset=0.0):
     if x.is_cuda:
-        return _seq().resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale)
-    return ref.resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale)
+        return _seq().resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale, w_offset)
+    return ref.resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale, w_offset)
 
 
 def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, k_cache, v_cache, slots):
@@ -178,23 +179,27 @@ def postnorm(x, y, alpha, w, eps, out_dtype):
 
 
 def qk_norm_rope_kv_write(qkv, num_heads, num_kv_heads, dim, v_dim, q_norm_w, k_norm_w, eps, positions, rot_dims,
-                          rot_base, k_cache, v_cache, slots):
+                          rot_base, k_cache, v_cache, slots, freqs=None, mag=1.0):
+    """num_kv_heads == 0: the rows hold queries only (keys and values are another layer's); `freqs` (fp64 per
+    pair) and `mag`: scaled rotary frequencies and the factor on cos / sin."""
     fn = _seq().qk_norm_rope_kv_write if qkv.is_cuda else ref.qk_norm_rope_kv_write
     return fn(qkv, num_heads, num_kv_heads, dim, v_dim, q_norm_w, k_norm_w, eps, positions, rot_dims, rot_base,
-              k_cache, v_cache, slots)
+              k_cache, v_cache, slots, freqs, mag)
 
 
 def masked_attention(q, k_cache, v_cache, inp, scale, num_q_heads, head_dim, v_dim, window=None, chunk=None, sink=None,
-                     out_scale=1.0, out=None):
-    """Paged causal attention with a sliding window and / or a chunk mask, values of their own width."""
+                     out_scale=1.0, out=None, softcap=0.0):
+    """Paged causal attention with a sliding window and / or a chunk mask, values of their own width, an optional
+    per-head sink logit in the denominator and an optional tanh cap on the scaled scores."""
     if q.is_cuda:
         return _seq().window_attention(q, k_cache, v_cache, inp.block_table, inp.seq_lens, inp.query_start_loc,
                                        inp.positions, scale, num_q_heads, head_dim, window, sink,
                                        num_decode_seqs=inp.padded_tokens or inp.num_decode_seqs,
-                                       max_q_len=inp.max_q_len, chunk=chunk, v_dim=v_dim, out_scale=out_scale, out=out)
+                                       max_q_len=inp.max_q_len, chunk=chunk, v_dim=v_dim, out_scale=out_scale, out=out,
+                                       softcap=softcap)
     return ref.window_attention(q, k_cache, v_cache, inp.block_table, inp.seq_lens, inp.query_start_loc, scale,
                                 num_q_heads, head_dim, window, sink, chunk=chunk, v_dim=v_dim, out_scale=out_scale,
-                                out=out)
+                                out=out, softcap=softcap)
 
 
 def linear_state_scan(q, k, v, beta, a, neg_a, dt_bias, decay, state, inp, heads, qk_heads, dim, v_dim, silu_in,
@@ -284,9 +289,9 @@ def latent_attention(q_full, cache, inp, scale, rank):
     return ref.latent_attention(q_full, cache, inp.block_table, inp.seq_lens, inp.query_start_loc, scale, rank)
 
 
-def grouped_router(h, w, correction, top_k, n_groups, keep_groups, scale):
+def grouped_router(h, w, correction, top_k, n_groups, keep_groups, scale, score="softmax", group_top=1, renorm=True):
     fn = _lat().grouped_router if h.is_cuda else ref.grouped_router
-    return fn(h, w, correction, top_k, n_groups, keep_groups, scale)
+    return fn(h, w, correction, top_k, n_groups, keep_groups, scale, score, group_top, renorm)
 
 
 def glu_clamp(gu, limit, alpha=1.702):
@@ -305,3 +310,33 @@ def routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha=1.702
     if h.is_cuda:
         return _lat().routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha, n_all)
     return ref.routed_glu_experts(h, w13, w2, weights, ids, limit, alpha)
+
+
+# -- hashed pair embedding with a carried previous token, ungated squared-ReLU experts, scaled logits
+# (csrc/seq/pair_ops.cu) ---------------------------------------------------------------------------------------
+def _pair():
+    from gllm_b200.ops import sm100_pair
+    return sm100_pair
+
+
+def embedding_pair_hash(inp, table, pair_table, mul_prev, mul_cur, buckets, prev_state):
+    """fp32 stream: table[token] + pair_table[hash(previous token, token)]; the token before a portion's first row
+    is carried in prev_state [state slots] (None: no history, e.g. a memory probe)."""
+    slots = inp.rec_slots if prev_state is not None else None
+    fn = _pair().embedding_pair_hash if table.is_cuda else ref.embedding_pair_hash
+    return fn(inp.tokens, table, pair_table, mul_prev, mul_cur, buckets, inp.positions, prev_state, slots,
+              inp.query_start_loc)
+
+
+def routed_relu2_experts(h, w1, w2, weights, ids, grouped):
+    """sum_k weights[t, k] * down_e(relu(up_e h)^2); `grouped`: the grouped tcgen05 GEMM pair with the squared-ReLU
+    epilogue on the first product, otherwise the plain per-slot kernels."""
+    if h.is_cuda:
+        return _pair().routed_relu2_experts(h, w1, w2, weights, ids, grouped)
+    return ref.routed_relu2_experts(h, w1, w2, weights, ids)
+
+
+def scale_rows(z, scale):
+    if z.is_cuda:
+        return _pair().scale_rows(z, scale)
+    return ref.scale_rows(z, scale)

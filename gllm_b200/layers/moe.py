@@ -336,3 +336,39 @@ class GroupedGLUMoE(nn.Module):
             gu = ref.interleave_gate_up(gu, 64)
         self.w13.data[e].copy_(gu)
         self.w2.data[e].copy_(down)
+
+
+class GroupedRelu2MoE(nn.Module):
+    """Routed feed-forward whose router scores every expert by itself: s = sigmoid(router logits) in fp32, a
+    correction added for the choice only, group-limited choice (a group's score is the sum of its `group_top`
+    largest corrected scores, only the best `keep_groups` groups stay eligible), the `top_k` best eligible experts,
+    weighted by their plain scores s (`renorm`: divided by their sum) times `scale`. Every expert is ungated:
+    down(relu(up h)^2), no biases. One GPU. On CUDA in bf16 with ff % 8 == 0 and hidden % 8 == 0 the experts run as
+    the grouped tcgen05 GEMM pair (align + gather, up GEMM with the squared-ReLU epilogue, down GEMM, combine),
+    otherwise on the plain per-slot kernels (true fp32 for fp32 weights)."""
+
+    def __init__(self, num_experts: int, top_k: int, hidden: int, ff: int, n_groups: int, keep_groups: int, dtype,
+                 device, group_top: int = 2, renorm: bool = False, scale: float = 1.0, correction: bool = True):
+        super().__init__()
+        assert 1 <= top_k <= num_experts and n_groups >= 1 and num_experts % n_groups == 0 and \
+            1 <= keep_groups <= n_groups, (num_experts, top_k, n_groups, keep_groups)
+        assert top_k <= keep_groups * (num_experts // n_groups), "fewer eligible experts than choices"
+        self.num_experts, self.top_k, self.hidden, self.ff = num_experts, top_k, hidden, ff
+        self.n_groups, self.keep_groups, self.group_top, self.renorm, self.scale = \
+            n_groups, keep_groups, int(group_top), bool(renorm), float(scale)
+        self.router_w = _param(num_experts, hidden, dtype=dtype, device=device)
+        self.correction = nn.Parameter(torch.zeros(num_experts, dtype=torch.float32, device=device),
+                                       requires_grad=False) if correction else None
+        self.w1 = _param(num_experts, ff, hidden, dtype=dtype, device=device)
+        self.w2 = _param(num_experts, hidden, ff, dtype=dtype, device=device)
+        self.grouped = torch.device(device).type == "cuda" and dtype == torch.bfloat16 and ff % 8 == 0 and \
+            hidden % 8 == 0
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        w, ids = Fn.grouped_router(h, self.router_w, self.correction, self.top_k, self.n_groups, self.keep_groups,
+                                   self.scale, "sigmoid", self.group_top, self.renorm)
+        return Fn.routed_relu2_experts(h, self.w1, self.w2, w, ids, self.grouped)
+
+    def load_expert(self, e: int, up: torch.Tensor, down: torch.Tensor):
+        self.w1.data[e].copy_(up)
+        self.w2.data[e].copy_(down)

@@ -2,7 +2,8 @@
 of the input projection it reads (`in_names`, `in_rows`), the width of what it hands to the output projection
 (`n_out`), what it keeps in the cache (`cache_entry`) and a `core(inp, proj, cache, run_id, out, out_scale)` step.
 
-`CoreMixer` wraps cores that read the same input: ONE input GEMM over the concatenated projection rows, each core
+`CoreMixer` wraps cores that read the same input: ONE input GEMM over the concatenated projection rows (with the
+projections' biases in its epilogue, for cores that have them), each core
 writes scale_i * result_i into its column slice of one buffer, ONE output GEMM over the concatenated output
 projections — sum_i scale_i * o_i(core_i(h)). With a single core it is the plain mixer.
 """
@@ -27,6 +28,9 @@ class CoreMixer(nn.Module):
         n_in_pad = (self.n_in + 7) // 8 * 8            # the tensor-core GEMM wants N % 8 == 0; pad rows stay zero
         self.in_w = nn.Parameter(torch.zeros(n_in_pad, hidden, dtype=dtype, device=device), requires_grad=False)
         self.o_w = nn.Parameter(torch.zeros(hidden, self.n_out, dtype=dtype, device=device), requires_grad=False)
+        # biases of the input projection ('<projection>.b'), for cores that declare `has_bias`; rows of others stay 0
+        self.in_b = nn.Parameter(torch.zeros(n_in_pad, dtype=dtype, device=device), requires_grad=False) \
+            if any(getattr(c, "has_bias", False) for c in cores) else None
         self.uses_pages = any(c.uses_pages for c in cores)
         self.uses_state = any(c.uses_state for c in cores)
 
@@ -39,7 +43,7 @@ class CoreMixer(nn.Module):
         return {"kind": "multi", "kv": kv[0] if kv else None, "rec": rec[0] if rec else None}
 
     def forward(self, inp, h: torch.Tensor, cache, run_id: int) -> torch.Tensor:
-        proj = Fn.linear_any(h, self.in_w)
+        proj = Fn.linear_any(h, self.in_w, self.in_b)
         joint = torch.empty(h.shape[0], self.n_out, dtype=h.dtype, device=h.device)
         ci = co = 0
         for c, s in zip(self.cores, self.scales):
@@ -49,13 +53,18 @@ class CoreMixer(nn.Module):
 
     def load(self, reader, pre: str, put):
         """Checkpoint names: '<pre><core name>.<projection>' ('<pre><projection>' for a nameless single core)."""
-        rows, cols = [], []
+        rows, cols, at = [], [], 0
         for c, name in zip(self.cores, self.names):
             p = pre + (name + "." if name else "")
             for n, r in zip(c.in_names, c.in_rows):
                 t = reader.get(p + n)
                 assert t.shape[0] == r, (p + n, tuple(t.shape), r)
                 rows.append(t)
+                if getattr(c, "has_bias", False):
+                    b = reader.get(p + n + ".b")
+                    assert tuple(b.shape) == (r,), (p + n + ".b", tuple(b.shape), r)
+                    self.in_b.data[at:at + r].copy_(b)
+                at += r
             cols.append(reader.get(p + "o"))
             c.load_extra(reader, p, put)
         w = torch.cat(rows, 0)

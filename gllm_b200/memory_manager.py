@@ -59,6 +59,11 @@ class HybridCache:
                                                         attention: [latent | rotated key part]), paged like one KV
                                                         head; v_cache[r] is None (the values are columns of the row)
       {"kind": "multi", "kv": entry | None, "rec": entry | None}   -> a run that keeps both pages and state
+      {"kind": "shared", "source": r0}               -> no storage: k_cache[r] and v_cache[r] ARE those of run r0 (a
+                                                        layer that attends over an earlier layer's keys and values)
+      {"kind": "tokens"}                             -> token_state [slots] int32: the last token of every sequence
+                                                        (an embedding that looks at the previous token); listed after
+                                                        the runs
     Slot contents are never cleared on re-use: the kernels start from zeros for a chunk at position 0."""
 
     @staticmethod
@@ -70,6 +75,8 @@ class HybridCache:
             return e, None
         if e["kind"] in ("ssm", "linear"):
             return None, e
+        if e["kind"] in ("shared", "tokens"):
+            return None, None
         raise ValueError(e["kind"])
 
     @staticmethod
@@ -84,9 +91,14 @@ class HybridCache:
         self.num_layers = len(layout)
         self.use_mla = False
         self.k_cache, self.v_cache, self.conv_state, self.ssm_state = [], [], [], []
+        self.token_state = None
         for e in layout:
             k = v = cs = ss = None
             kv, rec = self._parts(e)
+            if e["kind"] == "shared":
+                k, v = self.k_cache[e["source"]], self.v_cache[e["source"]]
+            elif e["kind"] == "tokens":
+                self.token_state = torch.zeros(max(num_slots, 1), dtype=torch.int32, device=device)
             if kv is not None and kv["kind"] == "latent":
                 k = torch.zeros(kv_cache_shape(num_pages, 1, kv["dim"], page_size), dtype=dtype, device=device)
             elif kv is not None:
@@ -119,6 +131,8 @@ class HybridCache:
             if rec is not None:
                 cshape, sshape = HybridCache._rec_shapes(rec)
                 total += math.prod(cshape) * dtype_bytes + 4 * math.prod(sshape)
+            elif e["kind"] == "tokens":
+                total += 4
         return total
 
 

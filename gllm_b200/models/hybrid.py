@@ -5,7 +5,11 @@ feed-forward), and norm-after-sum blocks (architecture `Femolix`: gated delta ru
 chunk-masked rotary attention beside constant-decay linear attention, gated SiLU feed-forward, dense or routed, capped
 logits), and branch-norm blocks with a layer scale (architecture `Bevovik`: real-gated linear recurrent units,
 key-decay gated linear attention and latent attention with YaRN rotary, a grouped mixture of clamped gated experts
-with identity experts and a shared expert):
+with identity experts and a shared expert); and sandwich blocks whose norm weights are stored around zero (architecture
+`Notadra`: rotary attention with biased projections, YaRN-scaled partial rotation, capped scores, a unit sink in the
+softmax denominator, values of their own width and layers that read an earlier layer's keys and values; a
+sigmoid-scored, group-limited mixture of ungated squared-ReLU experts; a hashed embedding of the (previous, current)
+token pair added to the token embedding; scaled logits):
 
     x = embed[token]
     per layer:  x += ls1 * rms(mixer(x)) * n1 ;  x += ls2 * rms(ff(x)) * n2            (sublayers read x itself)
@@ -35,10 +39,18 @@ norms, writes the stream back and emits it in the compute dtype for the next sub
 In the branch-norm form one kernel per sublayer (`Fn.resid_norm` with a layer scale) norms the branch, adds it into
 the stream and emits the stream in the compute dtype for the next sublayer (the stream itself in fp32).
 
-config.json keys read here: architecture, vocab, width, embedding.scale, norm.eps, loop.{start,stop,times},
+Notadra (the sandwich form with gains 1 + w):
+
+    x = embed[token] + pair[(previous token * mul_prev + token * mul_cur) mod buckets]   (row `buckets` at position 0)
+    per layer:  x += rms(mixer(rms(x) (1 + n1))) (1 + n1b) ;  x += rms(ff(rms(x) (1 + n2))) (1 + n2b)
+    logits = logit_scale * head @ (rms(x) (1 + final_norm))
+
+config.json keys read here: architecture, vocab, width, embedding.scale, embedding.bigram.{buckets, mul_prev,
+mul_cur}, logit_scale, layers[i].mixer.{kv_from, softcap, rot.scaling.{factor, original, fast, slow}},
+norm.eps, loop.{start,stop,times},
 postln_alpha, logit_softcap, layers[i].{type, mixer{...}, mlp{kind, ff | expert.{ff, limit}, router.{experts, top,
-identity, scale, groups.{count, keep}}, shared.{ff, limit}} | null}, optional torch_dtype. Tensor names: embed, head,
-final.norm, l<i>.norm1|norm1b|norm2|norm2b|ls1|ls2, l<i>.mix.*, l<i>.mlp.up|down|gate|router|correction|
+identity, scale, groups.{count, keep}}, shared.{ff, limit}} | null}, optional torch_dtype. Tensor names: embed, bigram,
+head, l<i>.mix.{q,k,v}.b, l<i>.mlp.e<j>.{up,down}, final.norm, l<i>.norm1|norm1b|norm2|norm2b|ls1|ls2, l<i>.mix.*, l<i>.mlp.up|down|gate|router|correction|
 e<j>.{gate,up,down}|shared.{gate,up,down}.
 """
 from __future__ import annotations
@@ -52,7 +64,7 @@ from torch import nn
 from gllm_b200.layers import functional as Fn
 from gllm_b200.layers.latent_attention import LatentAttention
 from gllm_b200.layers.linear_attention import DecayLinearCore, GatedDeltaCore, KeyDecayLinearCore
-from gllm_b200.layers.moe import GroupedGLUMoE, SelectedSoftmaxMoE
+from gllm_b200.layers.moe import GroupedGLUMoE, GroupedRelu2MoE, SelectedSoftmaxMoE
 from gllm_b200.layers.parallel_mixer import CoreMixer
 from gllm_b200.layers.ssm import Mamba1Mixer, RGLRUMixer
 from gllm_b200.layers.window_attention import RotaryChunkCore, SinkWindowAttention
@@ -81,6 +93,10 @@ class HybridSpec:
     # "relu2": down(relu(up h)^2) | "silu_gate": down(silu(gate h) * up h) | "glu_clamp": clamped gate and up,
     # down(g sigmoid(1.702 g) (u + 1))
     ff_act: str = "relu2"
+    norm_offset: float = 0.0           # added to every norm weight in fp32 (1.0: weights stored around zero)
+    logit_scale: float = 1.0
+    # {"buckets", "mul_prev", "mul_cur"}: a second embedding table indexed by a hash of the (previous, current) pair
+    pair_hash: Optional[dict] = None
     eos_token_id: Optional[object] = None
     use_mla: bool = False
     quant: Optional[str] = None
@@ -123,6 +139,19 @@ def spec_bevovik(cfg) -> HybridSpec:
                       dtype=_DTYPES[dt], block="branchnorm", ff_act="glu_clamp", eos_token_id=cfg.get("eos_token_id"))
 
 
+def spec_notadra(cfg) -> HybridSpec:
+    dt = cfg.get("torch_dtype", cfg.get("dtype", "bfloat16"))
+    if dt not in _DTYPES:
+        raise ValueError(f"unsupported dtype {dt} for this architecture (bfloat16 | float32)")
+    bg = (cfg.get("embedding") or {}).get("bigram")
+    pair = {k: int(bg[k]) for k in ("buckets", "mul_prev", "mul_cur")} if bg else None
+    return HybridSpec(arch="notadra", hidden_size=int(cfg["width"]), vocab_size=int(cfg["vocab"]),
+                      rms_eps=float(cfg["norm"]["eps"]), embed_scale=1.0, layers=[dict(x) for x in cfg["layers"]],
+                      dtype=_DTYPES[dt], block="sandwich", ff_act="relu2", norm_offset=1.0,
+                      logit_scale=float(cfg.get("logit_scale", 1.0)), pair_hash=pair,
+                      eos_token_id=cfg.get("eos_token_id"))
+
+
 def layer_runs(n_layers: int, start: int, stop: int, times: int):
     """[(layer index, add_embed)] in execution order; add_embed marks the first layer of every pass but the first."""
     if times <= 1 or stop <= start:
@@ -147,6 +176,15 @@ class Relu2MLP(nn.Module):
 
 def make_mixer(kind: str, m: dict, spec: HybridSpec, device):
     h, dt = spec.hidden_size, spec.dtype
+    if kind == "attention" and spec.arch == "notadra":
+        rot = m.get("rot") or {}
+        src = m.get("kv_from")
+        core = RotaryChunkCore(int(m["heads"]), int(m.get("kv_heads", m["heads"])), int(m["dim"]),
+                               int(m.get("vdim", m["dim"])), float(m["scale"]), int(rot.get("dims", 0)),
+                               float(rot.get("base", 10000.0)), None, None, spec.rms_eps, dt, device, qk_norm=False,
+                               rot_scaling=rot.get("scaling"), softcap=float(m.get("softcap") or 0.0), unit_sink=True,
+                               bias=True, kv_from=int(src) if src is not None else None)
+        return CoreMixer(h, [core], [""], [1.0], dt, device)
     if kind == "attention":
         assert int(m.get("vdim", m["dim"])) == int(m["dim"]), "values are the keys: vdim must equal dim"
         window = (m.get("mask") or {}).get("size")
@@ -215,6 +253,12 @@ def make_ff(mlp: dict, spec: HybridSpec, device):
     kind = mlp.get("kind", "dense")
     if kind == "dense":
         return (GatedMLP if spec.ff_act == "silu_gate" else Relu2MLP)(h, int(mlp["ff"]), dt, device)
+    if kind == "moe" and spec.ff_act == "relu2":
+        r = mlp["router"]
+        groups = r.get("groups") or {}
+        count = int(groups.get("count", 1))
+        return GroupedRelu2MoE(int(r["experts"]), int(r["top"]), h, int(mlp["expert"]["ff"]), count,
+                               int(groups.get("keep", count)), dt, device, group_top=2, renorm=False)
     if kind == "moe" and spec.ff_act == "silu_gate":
         return SelectedSoftmaxMoE(int(mlp["router"]["experts"]), int(mlp["router"]["top"]), h,
                                   int(mlp["expert"]["ff"]), dt, device)
@@ -268,11 +312,15 @@ class HybridLM(nn.Module):
         self.device = torch.device(device)
         h, dt = spec.hidden_size, spec.dtype
         self.embed_w = nn.Parameter(torch.zeros(spec.vocab_size, h, dtype=dt, device=device), requires_grad=False)
+        self.pair_w = nn.Parameter(torch.zeros(spec.pair_hash["buckets"] + 1, h, dtype=dt, device=device),
+                                   requires_grad=False) if spec.pair_hash else None
         self.layers = nn.ModuleList([HybridLayer(spec, i, device) for i in range(spec.num_layers)])
         self.final_norm_w = nn.Parameter(torch.ones(h, dtype=dt, device=device), requires_grad=False)
         self.lm_head_w = nn.Parameter(torch.zeros(spec.vocab_size, h, dtype=dt, device=device), requires_grad=False)
         self.runs = layer_runs(spec.num_layers, spec.loop_start, spec.loop_stop, spec.loop_times)
-        self.has_state = any(getattr(l.mixer, "uses_state", not l.mixer.uses_pages) for l in self.layers)
+        # the pair embedding keeps every sequence's last token in its state slot
+        self.has_state = any(getattr(l.mixer, "uses_state", not l.mixer.uses_pages) for l in self.layers) or \
+            spec.pair_hash is not None
         self.has_pages = any(l.mixer.uses_pages for l in self.layers)
         self.needs_tok_seq = any(getattr(l.mixer, "needs_tok_seq", False) for l in self.layers)
         self.trace: Optional[list] = None     # debugging: when a list, the stream after every layer run is appended
@@ -285,8 +333,25 @@ class HybridLM(nn.Module):
     def hidden_size(self): return self.spec.hidden_size
 
     def cache_layout(self):
-        """One entry per layer RUN (a looped layer has one per pass)."""
-        return [self.layers[i].mixer.cache_entry() for i, _ in self.runs]
+        """One entry per layer RUN (a looped layer has one per pass). A mixer that reads another layer's pages
+        ({"kind": "shared", "layer": j}) is resolved to that layer's latest run before it ("source": run index);
+        with a pair embedding one more entry {"kind": "tokens"} follows the runs (the carried previous token)."""
+        out, last_run = [], {}
+        for r, (i, _) in enumerate(self.runs):
+            e = self.layers[i].mixer.cache_entry()
+            if e["kind"] == "shared":
+                j = e["layer"]
+                assert j in last_run, f"layer {i} reads the keys and values of layer {j}, which has not run before it"
+                src = out[last_run[j]]
+                assert src["kind"] == "kv", f"layer {j} keeps no keys and values of its own"
+                m, ms = self.layers[i].mixer.cores[0], self.layers[j].mixer.cores[0]
+                assert (m.kv_heads, m.dim, m.v_dim) == (ms.kv_heads, ms.dim, ms.v_dim), "shared pages: sizes differ"
+                e = {"kind": "shared", "source": last_run[j]}
+            out.append(e)
+            last_run[i] = r
+        if self.spec.pair_hash is not None:
+            out.append({"kind": "tokens"})
+        return out
 
     # -- forward ----------------------------------------------------------------------------------
     def forward(self, inp, cache, tpc=None, hidden=None, residual=None, **_):
@@ -295,28 +360,34 @@ class HybridLM(nn.Module):
             return self._forward_postnorm(inp, cache), None
         if spec.block == "branchnorm":
             return self._forward_branchnorm(inp, cache), None
-        x0 = Fn.embedding_scaled(inp.tokens, self.embed_w, spec.embed_scale)
+        off = spec.norm_offset
+        if spec.pair_hash is not None:
+            ph = spec.pair_hash
+            x0 = Fn.embedding_pair_hash(inp, self.embed_w, self.pair_w, ph["mul_prev"], ph["mul_cur"], ph["buckets"],
+                                        cache.token_state if cache is not None else None)
+        else:
+            x0 = Fn.embedding_scaled(inp.tokens, self.embed_w, spec.embed_scale)
         x = x0.clone() if any(a for _, a in self.runs) else x0
         n = len(self.runs)
         h = Fn.resid_norm(x, None, None, None, self.layers[self.runs[0][0]].norm1_w if n else self.final_norm_w,
-                          eps, dt)
+                          eps, dt, False, None, off)
         for r, (li, _) in enumerate(self.runs):
             L = self.layers[li]
             y = L.mixer(inp, h, cache, r)
             post = L.norm1b_w
             if L.mlp is not None:
-                h = Fn.resid_norm(x, y, post, None, L.norm2_w, eps, dt)
+                h = Fn.resid_norm(x, y, post, None, L.norm2_w, eps, dt, False, None, off)
                 y = L.mlp(h)
                 post = L.norm2b_w
             last = r + 1 == n
             w_pre = self.final_norm_w if last else self.layers[self.runs[r + 1][0]].norm1_w
             add = x0 if (not last and self.runs[r + 1][1]) else None
             if self.trace is not None:
-                Fn.resid_norm(x, y, post, None, None, eps, dt)
+                Fn.resid_norm(x, y, post, None, None, eps, dt, False, None, off)
                 self.trace.append(x.clone())
-                h = Fn.resid_norm(x, None, None, add, w_pre, eps, dt)
+                h = Fn.resid_norm(x, None, None, add, w_pre, eps, dt, False, None, off)
             else:
-                h = Fn.resid_norm(x, y, post, add, w_pre, eps, dt)
+                h = Fn.resid_norm(x, y, post, add, w_pre, eps, dt, False, None, off)
         return h, None
 
     def _forward_postnorm(self, inp, cache):
@@ -361,6 +432,8 @@ class HybridLM(nn.Module):
     def compute_logits(self, inp, hidden, tpc=None, all_rows: bool = False, local: bool = False):
         rows = hidden if all_rows else hidden.index_select(0, inp.logits_idx.long())
         z = Fn.linear_any(rows, self.lm_head_w)
+        if self.spec.logit_scale != 1.0:
+            z = Fn.scale_rows(z, self.spec.logit_scale)
         return Fn.softcap(z, self.spec.logit_softcap) if self.spec.logit_softcap > 0 else z
 
     # -- weights ----------------------------------------------------------------------------------
@@ -382,7 +455,9 @@ class HybridLM(nn.Module):
 
         for name, p in self.named_parameters():
             if name.endswith("norm_w") or "norm1" in name or "norm2" in name:
-                p.data.fill_(1.0)
+                p.data.fill_(1.0 - self.spec.norm_offset)
+            elif name.endswith("in_b") or name.endswith("correction"):
+                rnd(p, 0.1)
             elif name.endswith(".a"):
                 p.data.copy_(-torch.exp(torch.rand(p.shape, generator=g) * 2.0 - 1.0))
             elif name.endswith("dt_b"):
@@ -412,6 +487,8 @@ class HybridLM(nn.Module):
             param.data.copy_(t)
 
         put(self.embed_w, reader.get("embed"))
+        if self.pair_w is not None:
+            put(self.pair_w, reader.get("bigram"))
         for n, L in enumerate(self.layers):
             pre = f"l{L.layer_id}."
             put(L.norm1_w, reader.get(pre + "norm1"))
@@ -450,7 +527,13 @@ class HybridLM(nn.Module):
                 f = L.mlp
                 if L.ls2 is not None:
                     put(L.ls2, reader.get(pre + "ls2").float())
-                if isinstance(f, GroupedGLUMoE):
+                if isinstance(f, GroupedRelu2MoE):
+                    put(f.router_w, reader.get(pre + "mlp.router"))
+                    if f.correction is not None:
+                        put(f.correction, reader.get(pre + "mlp.correction").float())
+                    for e in range(f.num_experts):
+                        f.load_expert(e, reader.get(f"{pre}mlp.e{e}.up"), reader.get(f"{pre}mlp.e{e}.down"))
+                elif isinstance(f, GroupedGLUMoE):
                     put(f.router_w, reader.get(pre + "mlp.router"))
                     put(f.correction, reader.get(pre + "mlp.correction").float())
                     for e in range(f.num_experts):
@@ -487,3 +570,7 @@ def build_femolix(cfg, device):
 
 def build_bevovik(cfg, device):
     return HybridLM(spec_bevovik(cfg), device)
+
+
+def build_notadra(cfg, device):
+    return HybridLM(spec_notadra(cfg), device)

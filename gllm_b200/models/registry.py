@@ -4,7 +4,8 @@ Supported `architectures[0]` values:
   LlamaForCausalLM, Qwen2ForCausalLM, Qwen3ForCausalLM, Qwen2MoeForCausalLM, Qwen3MoeForCausalLM,
   MixtralForCausalLM, ChatGLMModel / ChatGLMForConditionalGeneration, DeepseekV2ForCausalLM,
   DeepseekV3ForCausalLM, Qwen2_5_VLForConditionalGeneration, Qwen3VLForConditionalGeneration,
-  Qwen3VLMoeForConditionalGeneration, Saritar, Femolix and Bevovik (layer-list decoders, models/hybrid.py).
+  Qwen3VLMoeForConditionalGeneration, Saritar, Femolix, Bevovik and Notadra (layer-list decoders,
+  models/hybrid.py).
 """
 from __future__ import annotations
 
@@ -171,6 +172,11 @@ def _build_bevovik(cfg, device):
     return build_bevovik(cfg, device)
 
 
+def _build_notadra(cfg, device):
+    from gllm_b200.models.hybrid import build_notadra
+    return build_notadra(cfg, device)
+
+
 def _build_femolix(cfg, device):
     from gllm_b200.models.hybrid import build_femolix
     return build_femolix(cfg, device)
@@ -180,6 +186,7 @@ ARCHITECTURES: Dict[str, Callable] = {
     "Saritar": _build_saritar,
     "Femolix": _build_femolix,
     "Bevovik": _build_bevovik,
+    "Notadra": _build_notadra,
     "LlamaForCausalLM": _build_decoder(spec_llama),
     "MistralForCausalLM": _build_decoder(spec_llama),
     "Qwen2ForCausalLM": _build_decoder(spec_qwen2),

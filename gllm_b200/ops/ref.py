@@ -466,14 +466,15 @@ def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> to
 
 def resid_norm(x: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torch.Tensor],
                add: Optional[torch.Tensor], w_pre: Optional[torch.Tensor], eps: float, out_dtype,
-               emit_plain: bool = False, post_scale: Optional[torch.Tensor] = None):
+               emit_plain: bool = False, post_scale: Optional[torch.Tensor] = None, w_offset: float = 0.0):
     """In place on the fp32 stream x [T, W]:  x += rms(y) * w_post ;  x += add ;  returns rms(x) * w_pre cast to
     `out_dtype` (None when w_pre is None). Every step is optional. All arithmetic in fp32. `post_scale` [W] fp32
     (a layer scale) multiplies the normed branch element by element: x += rms(y) * w_post * post_scale. `emit_plain` (with w_pre None): returns the stream itself rounded to
-    `out_dtype` — x for fp32 — for sublayers that read the stream without a norm in front."""
+    `out_dtype` — x for fp32 — for sublayers that read the stream without a norm in front. `w_offset` is added to
+    both norm weights in fp32 (1.0 for weights stored around zero)."""
     if y is not None:
         yf = y.float()
-        br = yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + eps) * w_post.float()
+        br = yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + eps) * (w_post.float() + w_offset)
         x += br * post_scale.float() if post_scale is not None else br
     if add is not None:
         x += add
@@ -481,7 +482,7 @@ def resid_norm(x: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torc
         if emit_plain:
             return x if out_dtype == torch.float32 else x.to(out_dtype)
         return None
-    return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * w_pre.float()).to(out_dtype)
+    return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * (w_pre.float() + w_offset)).to(out_dtype)
 
 
 def _cache_rows_write(cache: torch.Tensor, slots: torch.Tensor, rows: torch.Tensor):
@@ -515,12 +516,13 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                      seq_lens: torch.Tensor, query_start_loc: torch.Tensor, scale: float, num_q_heads: int,
                      head_dim: int, window: Optional[int], sink: Optional[torch.Tensor],
                      chunk: Optional[int] = None, v_dim: Optional[int] = None, out_scale: float = 1.0,
-                     out: Optional[torch.Tensor] = None) -> torch.Tensor:
+                     out: Optional[torch.Tensor] = None, softcap: float = 0.0) -> torch.Tensor:
     """Causal paged attention where position i sees j with 0 <= i - j < window (None: all of the past), and, with
     `chunk`, only j of its own chunk (floor(i / chunk) == floor(j / chunk), counted from position 0); the softmax
     denominator has one more term exp(sink[h]) that carries no value (None: plain softmax). Values may be wider or
     narrower than keys (`v_dim`); the result is multiplied by `out_scale` and written to `out` [T, H * v_dim] (any
-    row stride) when given."""
+    row stride) when given. `softcap` > 0 bounds every scaled score: s <- softcap * tanh(s / softcap), before the
+    mask and the softmax."""
     t = q.shape[0]
     hq, d = num_q_heads, head_dim
     dv = d if v_dim is None else v_dim
@@ -537,6 +539,8 @@ def window_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         vv = gather_kv(v_cache, block_table[s], sl[s]).float().repeat_interleave(g, dim=1)
         qq = q[q0:q1].reshape(ql, hq, d).float()
         att = torch.einsum("qhd,khd->hqk", qq, kk) * scale
+        if softcap > 0:
+            att = softcap * torch.tanh(att / softcap)
         qi = torch.arange(ql, device=q.device).view(ql, 1) + (sl[s] - ql)
         kj = torch.arange(sl[s], device=q.device).view(1, sl[s])
         dead = kj > qi
@@ -638,36 +642,48 @@ def postnorm(x: torch.Tensor, y: torch.Tensor, alpha: float, w: torch.Tensor, ep
     return x if out_dtype == torch.float32 else x.to(out_dtype)
 
 
-def rotate_half_pairs(x: torch.Tensor, positions: torch.Tensor, rot_dims: int, base: float) -> torch.Tensor:
+def rotate_half_pairs(x: torch.Tensor, positions: torch.Tensor, rot_dims: int, base: float,
+                      freqs: Optional[torch.Tensor] = None, mag: float = 1.0) -> torch.Tensor:
     """x [T, heads, D] fp32: entries i and i + rot_dims / 2 (i < rot_dims / 2) turn by positions * base^(-2i/rot_dims);
-    entries from rot_dims on pass through. Angles are formed in fp64."""
+    entries from rot_dims on pass through. Angles are formed in fp64. `freqs` [rot_dims / 2] fp64 replaces the
+    powers of the base (scaled frequencies); cos and sin are multiplied by `mag`."""
     if rot_dims <= 0:
         return x
     half = rot_dims // 2
-    freq = torch.exp2(-(2.0 * torch.arange(half, dtype=torch.float64, device=x.device) / rot_dims) * math.log2(base))
+    if freqs is not None:
+        freq = freqs.to(torch.float64)
+    else:
+        freq = torch.exp2(-(2.0 * torch.arange(half, dtype=torch.float64, device=x.device) / rot_dims) *
+                          math.log2(base))
     ang = positions.to(torch.float64)[:, None] * freq[None, :]
-    c, s = torch.cos(ang).float()[:, None, :], torch.sin(ang).float()[:, None, :]
+    c, s = (torch.cos(ang) * mag).float()[:, None, :], (torch.sin(ang) * mag).float()[:, None, :]
     a, b = x[..., :half], x[..., half:rot_dims]
     return torch.cat([a * c - b * s, b * c + a * s, x[..., rot_dims:]], -1)
 
 
 def qk_norm_rope_kv_write(qkv: torch.Tensor, num_heads: int, num_kv_heads: int, dim: int, v_dim: int, q_norm_w,
                           k_norm_w, eps: float, positions: torch.Tensor, rot_dims: int, rot_base: float,
-                          k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor) -> torch.Tensor:
+                          k_cache: torch.Tensor, v_cache: torch.Tensor, slots: torch.Tensor,
+                          freqs: Optional[torch.Tensor] = None, mag: float = 1.0) -> torch.Tensor:
     """qkv [T, >= H*D + G*D + G*Dv] = [queries | keys | values]. Per-head RMS norm of q and k (weights optional),
     then the rotate-half rotation of both; rotated keys go to the K cache, values as projected to the V cache.
-    Returns the queries [T, H * D]."""
+    Returns the queries [T, H * D]. With num_kv_heads == 0 the row holds queries only (a layer that reads another
+    layer's keys and values) and no cache is touched. `freqs`, `mag`: see `rotate_half_pairs`."""
     t = qkv.shape[0]
     hd, gd = num_heads * dim, num_kv_heads * dim
     q = qkv[:, :hd].reshape(t, num_heads, dim).float()
+    if num_kv_heads == 0:
+        if q_norm_w is not None:
+            q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm_w.float()
+        return rotate_half_pairs(q, positions, rot_dims, rot_base, freqs, mag).to(qkv.dtype).reshape(t, hd)
     k = qkv[:, hd:hd + gd].reshape(t, num_kv_heads, dim).float()
     v = qkv[:, hd + gd:hd + gd + num_kv_heads * v_dim].reshape(t, num_kv_heads, v_dim)
     if q_norm_w is not None:
         q = q * torch.rsqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm_w.float()
     if k_norm_w is not None:
         k = k * torch.rsqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm_w.float()
-    q = rotate_half_pairs(q, positions, rot_dims, rot_base)
-    k = rotate_half_pairs(k, positions, rot_dims, rot_base)
+    q = rotate_half_pairs(q, positions, rot_dims, rot_base, freqs, mag)
+    k = rotate_half_pairs(k, positions, rot_dims, rot_base, freqs, mag)
     _cache_rows_write(k_cache, slots, k.to(qkv.dtype))
     _cache_rows_write(v_cache, slots, v)
     return q.to(qkv.dtype).reshape(t, hd)
@@ -819,8 +835,8 @@ def rglru_scan(u: torch.Tensor, gates: torch.Tensor, gate_bias: torch.Tensor, c_
     return out
 
 
-def pair_rotary_frequencies(dims: int, base: float, scaling: Optional[dict] = None):
-    """-> (fp32 frequency per pair [dims / 2], factor on cos and sin). Pair i turns by position * base^(-2i/dims);
+def pair_rotary_frequencies(dims: int, base: float, scaling: Optional[dict] = None, dtype=torch.float32):
+    """-> (frequency per pair [dims / 2] in `dtype`, factor on cos and sin). Pair i turns by position * base^(-2i/dims);
     with YaRN `scaling` {factor, original, fast, slow}: where(t) = dims ln(original / (2 pi t)) / (2 ln base),
     lo = max(floor(where(fast)), 0), hi = min(ceil(where(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo,
     0.001), 0, 1), frequency f_i / factor * ramp_i + f_i (1 - ramp_i), magnitude 0.1 ln(factor) + 1."""
@@ -838,7 +854,7 @@ def pair_rotary_frequencies(dims: int, base: float, scaling: Optional[dict] = No
         ramp = ((i - lo) / max(hi - lo, 0.001)).clamp(0.0, 1.0)
         f = f / factor * ramp + f * (1.0 - ramp)
         mag = 0.1 * math.log(factor) + 1.0
-    return f.float(), float(mag)
+    return f.to(dtype), float(mag)
 
 
 def rotate_adjacent_pairs(x: torch.Tensor, positions: torch.Tensor, freqs: torch.Tensor, mag: float) -> torch.Tensor:
@@ -911,23 +927,29 @@ def latent_attention(q_full: torch.Tensor, cache: torch.Tensor, block_table: tor
 
 
 def grouped_router(h: torch.Tensor, w: torch.Tensor, correction: Optional[torch.Tensor], top_k: int, n_groups: int,
-                   keep_groups: int, scale: float):
-    """fp32 router: scores = softmax(h . w^T) over all outputs; choice = scores + correction; outputs form
-    `n_groups` equal groups of neighbours, a group's score is its largest choice score and only the best
-    `keep_groups` groups stay eligible (the others count as -inf); the top_k largest eligible choice scores are
-    chosen (ties: the lower index); weights = chosen scores / (their sum + 1e-20) * scale.
+                   keep_groups: int, scale: float, score: str = "softmax", group_top: int = 1,
+                   renorm: bool = True):
+    """fp32 router: scores = softmax(h . w^T) over all outputs (`score` "sigmoid": the logistic function of every
+    logit by itself); choice = scores + correction; outputs form `n_groups` equal groups of neighbours, a group's
+    score is the sum of its `group_top` largest choice scores (1: its largest) and only the best `keep_groups`
+    groups stay eligible (the others count as -inf); the top_k largest eligible choice scores are chosen (ties: the
+    lower index); weights = chosen scores / (their sum + 1e-20) * scale, or with `renorm` False the chosen scores
+    themselves * scale.
     -> (weights fp32 [T, k], ids int32 [T, k])"""
-    sc = torch.softmax(h.float() @ w.float().t(), -1)
+    z = h.float() @ w.float().t()
+    sc = torch.sigmoid(z) if score == "sigmoid" else torch.softmax(z, -1)
     choice = sc + correction.float() if correction is not None else sc
     t, n = sc.shape
     if n_groups > 1:
         per = n // n_groups
-        best = choice.reshape(t, n_groups, per).max(-1).values
+        best = torch.topk(choice.reshape(t, n_groups, per), min(group_top, per), dim=-1).values.sum(-1)
         kept = torch.topk(best, keep_groups, dim=-1).indices
         ok = torch.zeros(t, n_groups, dtype=torch.bool, device=h.device).scatter_(1, kept, True)
         choice = choice.masked_fill(~ok.repeat_interleave(per, 1), float("-inf"))
     ids = torch.topk(choice, top_k, dim=-1).indices
     sel = sc.gather(1, ids)
+    if not renorm:
+        return sel * scale, ids.to(torch.int32)
     return sel / (sel.sum(-1, keepdim=True) + 1e-20) * scale, ids.to(torch.int32)
 
 
@@ -967,3 +989,51 @@ def routed_glu_experts(h: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, wei
                 y = linear(a, w2[e]).float()
             out[rows] += weights[rows, kk].float().unsqueeze(1) * y
     return out.to(h.dtype)
+
+
+# ----------------------------------------------------------------------------------------------
+# hashed pair embedding with a carried previous token, ungated squared-ReLU experts, scaled logits
+# (PyTorch forms of the kernels in csrc/seq/pair_ops.cu)
+# ----------------------------------------------------------------------------------------------
+def embedding_pair_hash(ids: torch.Tensor, table: torch.Tensor, pair_table: torch.Tensor, mul_prev: int, mul_cur: int,
+                        buckets: int, positions: torch.Tensor, prev_state: Optional[torch.Tensor], rec_slots,
+                        query_start_loc: torch.Tensor) -> torch.Tensor:
+    """fp32 residual stream from token ids: table[id] + pair_table[(prev * mul_prev + id * mul_cur) mod buckets],
+    where prev is the token before in the same sequence; a token at position 0 takes row `buckets` (the last row).
+    The token before the first row of a portion that starts later comes from prev_state [slots] int32 at the
+    sequence's state slot, and the portion's last token is left there for the next step."""
+    x = table[ids.long()].float()
+    qsl = query_start_loc.tolist()
+    idl, pos = ids.tolist(), positions.tolist()
+    rows = []
+    for s in range(len(qsl) - 1):
+        q0, q1 = qsl[s], qsl[s + 1]
+        for r in range(q0, q1):
+            if pos[r] == 0:
+                rows.append(buckets)
+                continue
+            if r > q0:
+                prev = idl[r - 1]
+            else:
+                prev = int(prev_state[int(rec_slots[s])]) if prev_state is not None else 0
+            rows.append((prev * mul_prev + idl[r] * mul_cur) % buckets)
+        if prev_state is not None and q1 > q0:
+            prev_state[int(rec_slots[s])] = idl[q1 - 1]
+    return x + pair_table[torch.tensor(rows, dtype=torch.long, device=ids.device)].float()
+
+
+def routed_relu2_experts(h: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, weights: torch.Tensor,
+                         ids: torch.Tensor) -> torch.Tensor:
+    """sum_k weights[t, k] * down_e(relu(up_e h[t])^2) with e = ids[t, k]; w1 [E, F, W] (up), w2 [E, W, F] (down);
+    the activation is rounded to h's dtype between the two products."""
+    out = torch.zeros(h.shape, dtype=torch.float32, device=h.device)
+    for kk in range(ids.shape[1]):
+        for e in ids[:, kk].unique().tolist():
+            rows = (ids[:, kk] == e).nonzero().flatten()
+            a = relu2(linear(h[rows], w1[e]))
+            out[rows] += weights[rows, kk].float().unsqueeze(1) * linear(a, w2[e]).float()
+    return out.to(h.dtype)
+
+
+def scale_rows(z: torch.Tensor, scale: float) -> torch.Tensor:
+    return (z.float() * scale).to(z.dtype)
