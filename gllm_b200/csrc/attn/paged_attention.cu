@@ -44,7 +44,14 @@ struct AttnParams {
   int chunk;
   int64_t out_ts;
   float out_scale;
+  // score cap (cap_log2 > 0): a scaled score s becomes cap * tanh(s / cap) before the mask and the softmax;
+  // scale_over_cap = scale / cap, cap_log2 = cap * log2(e)
+  float cap_log2, scale_over_cap;
 };
+
+// tanh from exp and a division (this file is built with approximate intrinsics: the hardware tanh approximation
+// would cost the scores three more bits than this form does); +-1 at the ends, |error| ~ 1e-7 near 0
+__device__ __forceinline__ float tanh_exp(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
 
 template <int D>
 struct AttnSmem {
@@ -186,7 +193,7 @@ attn_decode_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_cons
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int col = abs0 + nt * 8 + (e & 1);
-        float v = sc[nt][e] * p.scale_log2;
+        float v = p.cap_log2 > 0.f ? p.cap_log2 * tanh_exp(sc[nt][e] * p.scale_over_cap) : sc[nt][e] * p.scale_log2;
         if (col >= seq_len || col < win_lo) v = -INFINITY;
         sc[nt][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -474,7 +481,7 @@ attn_prefill_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_con
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int col = abs0 + nt * 8 + (e & 1);
-        float v = sc[nt][e] * p.scale_log2;
+        float v = p.cap_log2 > 0.f ? p.cap_log2 * tanh_exp(sc[nt][e] * p.scale_over_cap) : sc[nt][e] * p.scale_log2;
         if (col > lim[e >> 1] || col < clo[e >> 1] || (p.window > 0 && col <= lim[e >> 1] - p.window)) v = -INFINITY;
         sc[nt][e] = v;
         mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -604,7 +611,12 @@ static int attn_decode_impl(const void* q, int64_t q_ts, void* out, const void* 
                             int64_t num_pages, const void* block_table, const void* seq_lens, void* part_o,
                             void* part_lse, int num_seqs, int seq_offset, int max_blocks, int Hq, int Hkv,
                             int D, int page_size, int num_splits, float scale, void* split_cnt, void* stream,
-                            int window, const void* sink, int chunk = 0, int64_t out_ts = 0, float out_scale = 1.0f) {
+                            int window, const void* sink, int chunk = 0, int64_t out_ts = 0, float out_scale = 1.0f,
+                            float softcap = 0.0f) {
+  if (softcap > 0.f && num_splits > 1) {
+    fprintf(stderr, "[gllm_b200] attn_decode: a score cap needs num_splits == 1\n");
+    return 1;
+  }
   if (sink != nullptr && num_splits > 1) {
     fprintf(stderr, "[gllm_b200] attn_decode: a softmax sink needs num_splits == 1\n");
     return 1;
@@ -633,6 +645,8 @@ static int attn_decode_impl(const void* q, int64_t q_ts, void* out, const void* 
   p.split_cnt = reinterpret_cast<uint32_t*>(split_cnt);
   p.window = window; p.sink = reinterpret_cast<const float*>(sink);
   p.chunk = chunk; p.out_ts = out_ts > 0 ? out_ts : (int64_t)Hq * D; p.out_scale = out_scale;
+  p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
   if ((chunk > 0 || out_scale != 1.0f || p.out_ts != (int64_t)Hq * D) && p.num_splits > 1) {
     fprintf(stderr, "[gllm_b200] attn_decode: chunk mask / scaled or strided output need num_splits == 1\n");
     return 1;
@@ -683,7 +697,8 @@ static int attn_prefill_impl(const void* q, int64_t q_ts, void* out, const void*
                              int64_t num_pages, const void* block_table, const void* seq_lens,
                              const void* q_start, int num_seqs, int seq_offset, int max_q_len, int max_blocks,
                              int Hq, int Hkv, int D, int page_size, float scale, void* stream, int window,
-                             const void* sink, int chunk = 0, int64_t out_ts = 0, float out_scale = 1.0f) {
+                             const void* sink, int chunk = 0, int64_t out_ts = 0, float out_scale = 1.0f,
+                             float softcap = 0.0f) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
   if (page_size < 8 || kTileN % page_size != 0 || Hq % Hkv != 0) {
     fprintf(stderr, "[gllm_b200] attn_prefill: unsupported page_size=%d / heads\n", page_size);
@@ -705,6 +720,8 @@ static int attn_prefill_impl(const void* q, int64_t q_ts, void* out, const void*
   p.scale_log2 = scale * 1.4426950408889634f;
   p.split_cnt = nullptr; p.window = window; p.sink = reinterpret_cast<const float*>(sink);
   p.chunk = chunk; p.out_ts = out_ts > 0 ? out_ts : (int64_t)Hq * D; p.out_scale = out_scale;
+  p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (D) {
     case 64: return launch_prefill<64>(tk, tv, p, num_seqs, max_q_len, st);
@@ -738,10 +755,10 @@ GLLM_EXPORT int gllm_attn_decode_mask(const void* q, int64_t q_ts, void* out, in
                                       const void* v_cache, int64_t num_pages, const void* block_table,
                                       const void* seq_lens, int num_seqs, int seq_offset, int max_blocks, int Hq,
                                       int Hkv, int D, int page_size, float scale, int window, int chunk,
-                                      const void* sink, float out_scale, void* stream) {
+                                      const void* sink, float out_scale, float softcap, void* stream) {
   return attn_decode_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, nullptr, nullptr,
                           num_seqs, seq_offset, max_blocks, Hq, Hkv, D, page_size, 1, scale, nullptr, stream, window,
-                          sink, chunk, out_ts, out_scale);
+                          sink, chunk, out_ts, out_scale, softcap);
 }
 
 GLLM_EXPORT int gllm_attn_prefill_mask(const void* q, int64_t q_ts, void* out, int64_t out_ts, const void* k_cache,
@@ -749,8 +766,8 @@ GLLM_EXPORT int gllm_attn_prefill_mask(const void* q, int64_t q_ts, void* out, i
                                        const void* seq_lens, const void* q_start, int num_seqs, int seq_offset,
                                        int max_q_len, int max_blocks, int Hq, int Hkv, int D, int page_size,
                                        float scale, int window, int chunk, const void* sink, float out_scale,
-                                       void* stream) {
+                                       float softcap, void* stream) {
   return attn_prefill_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, q_start, num_seqs,
                            seq_offset, max_q_len, max_blocks, Hq, Hkv, D, page_size, scale, stream, window, sink,
-                           chunk, out_ts, out_scale);
+                           chunk, out_ts, out_scale, softcap);
 }

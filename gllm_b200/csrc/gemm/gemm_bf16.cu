@@ -63,6 +63,8 @@ struct GemmParams {
   // gated epilogue variant (kEpiSiluMul with glu_limit > 0): g = min(gate, limit), u = clamp(up, +-limit),
   // out = g * sigmoid(glu_alpha * g) * (u + 1) instead of silu(gate) * up
   float glu_limit, glu_alpha;
+  // plain-store epilogue activation: 0 none, 1 squared ReLU (max(x, 0)^2, after the bias)
+  int act;
   // split-K (decode-sized M): unit = (tile, k-slice); partials go through an fp32 workspace in a
   // thread-private layout, the last-arriving CTA of a tile sums them in slice order and runs the epilogue
   int split_k;
@@ -396,6 +398,10 @@ gemm_bf16_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                        b3 = unpack_bf16(bv.w);
                 f[0] += b0.x; f[1] += b0.y; f[2] += b1.x; f[3] += b1.y;
                 f[4] += b2.x; f[5] += b2.y; f[6] += b3.x; f[7] += b3.y;
+              }
+              if (p.act == 1) {
+#pragma unroll
+                for (int e = 0; e < 8; ++e) { const float r = fmaxf(f[e], 0.f); f[e] = r * r; }
               }
               stage_put((h + j) / 8, f);
             }
@@ -733,7 +739,7 @@ GLLM_EXPORT int gllm_gemm_bf16_batched(const void* A, int64_t lda_t, int64_t lda
 // epi: 0 store, 1 SiLU-gate (slab rows interleaved per 64 like the dense gate/up weight).
 static int moe_grouped_gemm_impl(const void* A, int64_t lda, const void* W, void* C, int64_t ldc, int max_tiles, int N,
                                  int K, int E, const void* tile_expert, const void* num_tiles_ptr, int epi,
-                                 const void* row_dest, void* stream, float glu_limit, float glu_alpha) {
+                                 const void* row_dest, void* stream, float glu_limit, float glu_alpha, int act = 0) {
   if (max_tiles <= 0) return 0;
   if ((K % 8) != 0 || (N % 8) != 0 || (lda % 8) != 0 || (ldc % 8) != 0) return 1;
   const int bn = 128;  // 64|64 gate/up interleave for the SiLU epilogue; good balance for expert tiles
@@ -753,6 +759,7 @@ static int moe_grouped_gemm_impl(const void* A, int64_t lda, const void* W, void
   p.row_dest = reinterpret_cast<const int64_t*>(row_dest);
   p.glu_limit = glu_limit;
   p.glu_alpha = glu_alpha;
+  p.act = act;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   return epi == kEpiSiluMul ? launch_gemm<128, kEpiSiluMul>(ta, tb, p, st) : launch_gemm<128, kEpiStore>(ta, tb, p, st);
 }
@@ -762,6 +769,16 @@ GLLM_EXPORT int gllm_moe_grouped_gemm(const void* A, int64_t lda, const void* W,
                                       const void* num_tiles_ptr, int epi, const void* row_dest, void* stream) {
   return moe_grouped_gemm_impl(A, lda, W, C, ldc, max_tiles, N, K, E, tile_expert, num_tiles_ptr, epi, row_dest,
                                stream, 0.f, 0.f);
+}
+
+// Grouped GEMM with the plain-store epilogue and an activation on the result (act 1: squared ReLU): the first
+// product of ungated experts.
+GLLM_EXPORT int gllm_moe_grouped_gemm_act(const void* A, int64_t lda, const void* W, void* C, int64_t ldc,
+                                          int max_tiles, int N, int K, int E, const void* tile_expert,
+                                          const void* num_tiles_ptr, int act, void* stream) {
+  if (act != 0 && act != 1) return 1;
+  return moe_grouped_gemm_impl(A, lda, W, C, ldc, max_tiles, N, K, E, tile_expert, num_tiles_ptr, kEpiStore, nullptr,
+                               stream, 0.f, 0.f, act);
 }
 
 // Grouped gate / up GEMM with the clamped gated epilogue (slab rows interleaved per 64).

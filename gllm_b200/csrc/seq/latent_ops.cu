@@ -306,13 +306,14 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(
 }
 
 // ------------------------------------------------------------------------------------------------
-// Grouped router selection, one warp per token over its fp32 logits [E]: scores = softmax over all E; choice =
-// score + correction; E / n_groups neighbours form a group whose score is its largest choice; only the `keep`
-// best groups stay eligible; the top_k largest eligible choices are taken (ties: the lower index); weights = the
-// chosen scores / (their sum + 1e-20) * scale.
+// Grouped router selection, one warp per token over its fp32 logits [E]: scores = softmax over all E (`sigmoid`:
+// 1 / (1 + exp(-logit)) of every logit by itself); choice = score + correction; E / n_groups neighbours form a group
+// whose score is the sum of its `group_top` largest choices (1: its largest); only the `keep` best groups stay
+// eligible; the top_k largest eligible choices are taken (ties: the lower index); weights = the chosen scores /
+// (their sum + 1e-20) * scale, or without `renorm` the chosen scores * scale.
 __global__ void __launch_bounds__(128) grouped_router_select_kernel(
     const float* __restrict__ logits, const float* __restrict__ correction, int ntok, int E, int top_k, int n_groups,
-    int keep, float scale, float* __restrict__ wout, int* __restrict__ ids) {
+    int keep, float scale, float* __restrict__ wout, int* __restrict__ ids, int sigmoid, int group_top, int renorm) {
   extern __shared__ float rs[];          // per warp: score [E], choice [E], group score [n_groups]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp;
@@ -321,23 +322,49 @@ __global__ void __launch_bounds__(128) grouped_router_select_kernel(
   float* choice = score + E;
   float* gscore = choice + E;
   const float* z = logits + (size_t)t * E;
-  float mx = -INFINITY;
-  for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
-  mx = warp_max(mx);
-  float den = 0.f;
-  for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - mx); score[e] = p; den += p; }
-  den = warp_sum(den);
-  for (int e = lane; e < E; e += 32) {
-    const float sc = score[e] / den;
-    score[e] = sc;
-    choice[e] = sc + (correction != nullptr ? correction[e] : 0.f);
+  if (sigmoid) {
+    for (int e = lane; e < E; e += 32) {
+      const float sc = 1.0f / (1.0f + expf(-z[e]));
+      score[e] = sc;
+      choice[e] = sc + (correction != nullptr ? correction[e] : 0.f);
+    }
+  } else {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = warp_max(mx);
+    float den = 0.f;
+    for (int e = lane; e < E; e += 32) { const float p = expf(z[e] - mx); score[e] = p; den += p; }
+    den = warp_sum(den);
+    for (int e = lane; e < E; e += 32) {
+      const float sc = score[e] / den;
+      score[e] = sc;
+      choice[e] = sc + (correction != nullptr ? correction[e] : 0.f);
+    }
   }
   __syncwarp();
   if (n_groups > 1) {
     const int per = E / n_groups;
     for (int g = lane; g < n_groups; g += 32) {
       float b = -INFINITY;
-      for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, choice[e]);
+      if (group_top <= 1 || per < 2) {
+        for (int e = g * per; e < (g + 1) * per; ++e) b = fmaxf(b, choice[e]);
+      } else {                                   // the sum of the group's largest `group_top` choices
+        float last = INFINITY;
+        int last_i = -1;
+        b = 0.f;
+        for (int r = 0; r < min(group_top, per); ++r) {
+          float m = -INFINITY;
+          int mi = -1;
+          for (int e = g * per; e < (g + 1) * per; ++e) {
+            const float v = choice[e];
+            const bool after = v < last || (v == last && e > last_i);       // not taken in an earlier round
+            if (after && (v > m || mi < 0)) { m = v; mi = e; }
+          }
+          b += m;
+          last = m;
+          last_i = mi;
+        }
+      }
       gscore[g] = b;
     }
     __syncwarp();
@@ -389,7 +416,9 @@ __global__ void __launch_bounds__(128) grouped_router_select_kernel(
   }
   __syncwarp();
   if (lane == 0)
-    for (int kk = 0; kk < top_k; ++kk) wout[(size_t)t * top_k + kk] = wout[(size_t)t * top_k + kk] / (sum + 1e-20f) * scale;
+    for (int kk = 0; kk < top_k; ++kk)
+      wout[(size_t)t * top_k + kk] = renorm ? wout[(size_t)t * top_k + kk] / (sum + 1e-20f) * scale
+                                            : wout[(size_t)t * top_k + kk] * scale;
 }
 
 // out[t, f] = g sigmoid(alpha g) (u + 1), g = min(gu[t, f], limit), u = clamp(gu[t, F + f], +-limit)
@@ -573,7 +602,7 @@ GLLM_EXPORT int gllm_lat_attention(const void* q, const void* cache, const void*
 
 GLLM_EXPORT int gllm_lat_grouped_router_select(const void* logits, const void* correction, int ntok, int E, int top_k,
                                                int n_groups, int keep, float scale, void* wout, void* ids,
-                                               void* stream) {
+                                               int sigmoid, int group_top, int renorm, void* stream) {
   if (ntok <= 0) return 0;
   if (top_k > E || E > 4096 || n_groups < 1 || E % n_groups != 0 || keep < 1 || keep > n_groups) return 2;
   cudaStream_t st = (cudaStream_t)stream;
@@ -582,7 +611,7 @@ GLLM_EXPORT int gllm_lat_grouped_router_select(const void* logits, const void* c
     cudaFuncSetAttribute(grouped_router_select_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   grouped_router_select_kernel<<<(ntok + 3) / 4, 128, smem, st>>>((const float*)logits, (const float*)correction,
                                                                   ntok, E, top_k, n_groups, keep, scale,
-                                                                  (float*)wout, (int*)ids);
+                                                                  (float*)wout, (int*)ids, sigmoid, group_top, renorm);
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }

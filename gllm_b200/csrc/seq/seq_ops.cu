@@ -32,12 +32,14 @@ __global__ void embed_scale_kernel(const int* __restrict__ ids, const T* __restr
 
 // x += rms(y) * w_post * post_scale ; x += add ; out = rms(x) * w_pre   (each part optional; post_scale: an fp32
 // layer scale). With emit_plain and no w_pre, out = x rounded to T (sublayers that read the stream un-normed).
+// w_off is added to both norm weights in fp32 (1 for weights stored around zero).
 template <typename T>
 __global__ void __launch_bounds__(256) resid_norm_kernel(float* __restrict__ x, const T* __restrict__ y, long ldy,
                                                          const T* __restrict__ w_post,
                                                          const float* __restrict__ post_scale,
                                                          const float* __restrict__ add, const T* __restrict__ w_pre,
-                                                         T* __restrict__ out, int width, float eps, int emit_plain) {
+                                                         T* __restrict__ out, int width, float eps, int emit_plain,
+                                                         float w_off) {
   __shared__ float scratch[8];
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * width;
@@ -54,7 +56,7 @@ __global__ void __launch_bounds__(256) resid_norm_kernel(float* __restrict__ x, 
   for (int i = threadIdx.x; i < width; i += 256) {
     float v = xr[i];
     if (y != nullptr) {
-      float br = to_f(y[(size_t)t * ldy + i]) * r_post * to_f(w_post[i]);
+      float br = to_f(y[(size_t)t * ldy + i]) * r_post * (to_f(w_post[i]) + w_off);
       if (post_scale != nullptr) br *= post_scale[i];
       v += br;
     }
@@ -66,7 +68,7 @@ __global__ void __launch_bounds__(256) resid_norm_kernel(float* __restrict__ x, 
   if (w_pre == nullptr) return;
   ss2 = block_sum<256>(ss2, scratch);
   const float r = 1.0f / sqrtf(ss2 / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += 256) out[(size_t)t * width + i] = from_f<T>(xr[i] * r * to_f(w_pre[i]));
+  for (int i = threadIdx.x; i < width; i += 256) out[(size_t)t * width + i] = from_f<T>(xr[i] * r * (to_f(w_pre[i]) + w_off));
 }
 
 
@@ -105,13 +107,14 @@ __global__ void qk_norm_kv_write_kernel(const T* __restrict__ qk, long ldqk, int
 // chunk, floor(i / chunk) == floor(j / chunk)); keys of width D, values of width Dv (their caches have their own
 // slab widths); the result is multiplied by out_scale and written with row stride ldo. One warp per (token, head);
 // 4 consecutive tokens of one head per block (their key ranges overlap, so K/V rows are shared through L1).
-// Scores: one key per lane; P.V: value entries across lanes.
+// Scores: one key per lane; P.V: value entries across lanes. softcap > 0: a scaled score s becomes
+// softcap * tanh(s / softcap) before the softmax.
 template <typename T, int MAXR>
 __global__ void __launch_bounds__(128) window_attn_kernel(
     const T* __restrict__ q, const T* __restrict__ kc, const T* __restrict__ vc, const int* __restrict__ block_table,
     int bt_stride, const int* __restrict__ qsl, const int* __restrict__ positions, int ntok, int nseq, float scale,
     int H, int G, int D, int Dv, int window, int chunk, const float* __restrict__ sink, T* __restrict__ out, long ldo,
-    float out_scale, int ps, int slab, int slab_v) {
+    float out_scale, int ps, int slab, int slab_v, float softcap) {
   __shared__ float qs[4][256];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * 4 + warp, h = blockIdx.y;
@@ -149,6 +152,7 @@ __global__ void __launch_bounds__(128) window_attn_kernel(
         for (int e = 0; e < slab; ++e) dot = fmaf(qq[e], to_f(kr[e]), dot);
       }
       sc = dot * scale;
+      if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
     }
     const float m_new = fmaxf(m, warp_max(sc));
     const float alpha = expf(m - m_new);          // m == -inf only before the first key: exp(-inf) == 0
@@ -317,10 +321,11 @@ __global__ void relu2_kernel(const T* __restrict__ x, T* __restrict__ out, size_
   }
 }
 
-// C[M, N] = A[M, K] . W[N, K]^T, fp32 accumulation in ascending k for every element
+// C[M, N] = A[M, K] . W[N, K]^T (+ bias[N], added to the fp32 sum), fp32 accumulation in ascending k for every element
 template <typename T, typename TO = T>
 __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ A, long lda, const T* __restrict__ W,
-                                                        long ldw, TO* __restrict__ Cm, long ldc, int M, int N, int K) {
+                                                        long ldw, TO* __restrict__ Cm, long ldc, int M, int N, int K,
+                                                        const T* __restrict__ bias = nullptr) {
   __shared__ float As[16][64 + 1], Ws[16][64 + 1];
   const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
   const int m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
@@ -349,7 +354,7 @@ __global__ void __launch_bounds__(256) gemm_simt_kernel(const T* __restrict__ A,
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int m = m0 + ty * 4 + i, n = n0 + tx * 4 + j;
-      if (m < M && n < N) Cm[(size_t)m * ldc + n] = from_f<TO>(acc[i][j]);
+      if (m < M && n < N) Cm[(size_t)m * ldc + n] = from_f<TO>(acc[i][j] + (bias != nullptr ? to_f(bias[n]) : 0.f));
     }
 }
 
@@ -376,11 +381,11 @@ template <typename T>
 int attn_dispatch(dim3 grid, cudaStream_t st, const void* q, const void* kc, const void* vc, const int* bt,
                   int bt_stride, const int* qsl, const int* pos, int ntok, int nseq, float scale, int H, int G, int D,
                   int Dv, int window, int chunk, const float* sink, void* out, long ldo, float out_scale, int ps,
-                  int slab, int slab_v) {
+                  int slab, int slab_v, float softcap) {
 #define GLLM_ATTN(R)                                                                                              \
   window_attn_kernel<T, R><<<grid, 128, 0, st>>>((const T*)q, (const T*)kc, (const T*)vc, bt, bt_stride, qsl, pos, \
                                                  ntok, nseq, scale, H, G, D, Dv, window, chunk, sink, (T*)out, ldo, \
-                                                 out_scale, ps, slab, slab_v)
+                                                 out_scale, ps, slab, slab_v, softcap)
   if (D > 256) return 2;
   if (Dv <= 32) GLLM_ATTN(1);
   else if (Dv <= 64) GLLM_ATTN(2);
@@ -411,17 +416,18 @@ GLLM_EXPORT int gllm_seq_embed_scale(const void* ids, const void* table, void* o
 
 GLLM_EXPORT int gllm_seq_resid_norm(void* x, const void* y, long ldy, const void* w_post, const void* post_scale,
                                     const void* add, const void* w_pre, void* out, int ntok, int width, float eps,
-                                    int emit_plain, int is_f32, void* stream) {
+                                    int emit_plain, int is_f32, float w_off, void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   GLLM_BY_DTYPE(is_f32,
                 (resid_norm_kernel<__nv_bfloat16><<<ntok, 256, 0, st>>>(
                     (float*)x, (const __nv_bfloat16*)y, ldy, (const __nv_bfloat16*)w_post, (const float*)post_scale,
-                    (const float*)add, (const __nv_bfloat16*)w_pre, (__nv_bfloat16*)out, width, eps, emit_plain)),
+                    (const float*)add, (const __nv_bfloat16*)w_pre, (__nv_bfloat16*)out, width, eps, emit_plain,
+                    w_off)),
                 (resid_norm_kernel<float><<<ntok, 256, 0, st>>>((float*)x, (const float*)y, ldy, (const float*)w_post,
                                                                 (const float*)post_scale, (const float*)add,
                                                                 (const float*)w_pre, (float*)out, width, eps,
-                                                                emit_plain)));
+                                                                emit_plain, w_off)));
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }
@@ -447,7 +453,7 @@ GLLM_EXPORT int gllm_seq_window_attention(const void* q, const void* kc, const v
                                           int bt_stride, const void* qsl, const void* positions, int ntok, int nseq,
                                           float scale, int H, int G, int D, int Dv, int window, int chunk,
                                           const void* sink, void* out, long ldo, float out_scale, int ps, int slab,
-                                          int slab_v, int is_f32, void* stream) {
+                                          int slab_v, int is_f32, float softcap, void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((ntok + 3) / 4, H);
@@ -455,11 +461,11 @@ GLLM_EXPORT int gllm_seq_window_attention(const void* q, const void* kc, const v
   if (is_f32)
     rc = attn_dispatch<float>(grid, st, q, kc, vc, (const int*)block_table, bt_stride, (const int*)qsl,
                               (const int*)positions, ntok, nseq, scale, H, G, D, Dv, window, chunk, (const float*)sink,
-                              out, ldo, out_scale, ps, slab, slab_v);
+                              out, ldo, out_scale, ps, slab, slab_v, softcap);
   else
     rc = attn_dispatch<__nv_bfloat16>(grid, st, q, kc, vc, (const int*)block_table, bt_stride, (const int*)qsl,
                                       (const int*)positions, ntok, nseq, scale, H, G, D, Dv, window, chunk,
-                                      (const float*)sink, out, ldo, out_scale, ps, slab, slab_v);
+                                      (const float*)sink, out, ldo, out_scale, ps, slab, slab_v, softcap);
   if (rc) return rc;
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
@@ -541,16 +547,17 @@ GLLM_EXPORT int gllm_seq_relu2(const void* x, void* out, long n, int is_f32, voi
 }
 
 GLLM_EXPORT int gllm_seq_gemm_simt(const void* a, long lda, const void* w, long ldw, void* c, long ldc, int M, int N,
-                                   int K, int is_f32, void* stream) {
+                                   int K, int is_f32, const void* bias, void* stream) {
   if (M <= 0 || N <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid((N + 63) / 64, (M + 63) / 64);
   GLLM_BY_DTYPE(is_f32,
                 (gemm_simt_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((const __nv_bfloat16*)a, lda,
                                                                       (const __nv_bfloat16*)w, ldw,
-                                                                      (__nv_bfloat16*)c, ldc, M, N, K)),
+                                                                      (__nv_bfloat16*)c, ldc, M, N, K,
+                                                                      (const __nv_bfloat16*)bias)),
                 (gemm_simt_kernel<float><<<grid, 256, 0, st>>>((const float*)a, lda, (const float*)w, ldw, (float*)c,
-                                                               ldc, M, N, K)));
+                                                               ldc, M, N, K, (const float*)bias)));
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }

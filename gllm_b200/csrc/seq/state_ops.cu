@@ -45,13 +45,15 @@ __global__ void __launch_bounds__(256) postnorm_kernel(float* __restrict__ x, co
 // One block per token; its warps walk the heads: [0, H) queries, [H, H + G) keys, [H + G, H + 2G) values (copied to
 // the V cache). q / k: RMS norm over D with a shared weight, then entries i and i + rot/2 (i < rot/2) turn by
 // pos * base^(-2i/rot). The token's cos / sin row is formed once per block, the angle in fp64 (no table, no maximum
-// position), the rotation itself in fp32.
+// position), the rotation itself in fp32. `freqs` (fp64, one per pair) replaces the powers of the base (scaled
+// frequencies); cos and sin are multiplied by `mag`. With G == 0 a row holds queries only (the keys and values are
+// another layer's) and no cache is touched.
 template <typename T>
 __global__ void __launch_bounds__(256) qk_norm_rope_kv_write_kernel(
     const T* __restrict__ qkv, long ld, int H, int G, int D, int Dv, const T* __restrict__ qn,
     const T* __restrict__ kn, float eps, const int* __restrict__ positions, int rot, double log2_base,
     T* __restrict__ q_out, T* __restrict__ kc, T* __restrict__ vc, const int* __restrict__ slots, int ps, int slab,
-    int slab_v) {
+    int slab_v, const double* __restrict__ freqs, float mag) {
   extern __shared__ float cs_tab[];      // [rot / 2] cos, then [rot / 2] sin
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x;
@@ -59,12 +61,12 @@ __global__ void __launch_bounds__(256) qk_norm_rope_kv_write_kernel(
   const double pos = (double)positions[t];
   for (int i = threadIdx.x; i < half; i += 256) {
     double sn, cs;
-    sincos(pos * exp2(-(2.0 * (double)i / (double)rot) * log2_base), &sn, &cs);
-    cs_tab[i] = (float)cs;
-    cs_tab[half + i] = (float)sn;
+    sincos(pos * (freqs != nullptr ? freqs[i] : exp2(-(2.0 * (double)i / (double)rot) * log2_base)), &sn, &cs);
+    cs_tab[i] = (float)(cs * (double)mag);
+    cs_tab[half + i] = (float)(sn * (double)mag);
   }
   __syncthreads();
-  const int slot = slots[t];
+  const int slot = G > 0 ? slots[t] : -1;
   for (int head = warp; head < H + 2 * G; head += 8) {
     if (head >= H + G) {
       if (slot < 0) continue;
@@ -469,18 +471,27 @@ __global__ void __launch_bounds__(128) router_select_kernel(const float* __restr
 
 // plain experts, first half: act[slot, f] = silu(gate_e[f] . h) * (up_e[f] . h); one warp per (slot, f). With
 // limit > 0 the clamped form: g = min(gate, limit), u = clamp(up, +-limit), act = g sigmoid(alpha g) (u + 1).
-// An id >= n_real names an identity expert: nothing to compute here.
+// An id >= n_real names an identity expert: nothing to compute here. With `ungated` the experts have no gate:
+// w13 is [E, F, width] (up rows only) and act = relu(up_e[f] . h)^2.
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gate_up_kernel(const T* __restrict__ h, long ldh,
                                                           const T* __restrict__ w13, const int* __restrict__ ids,
                                                           int top_k, int width, int F, T* __restrict__ act,
-                                                          int n_real, float limit, float alpha) {
+                                                          int n_real, float limit, float alpha, int ungated) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int slot = blockIdx.x, f = blockIdx.y * 4 + warp;
   if (f >= F) return;
   const int e = ids[slot];
   if (e >= n_real) return;
   const T* hr = h + (size_t)(slot / top_k) * ldh;
+  if (ungated) {
+    const T* ur = w13 + ((size_t)e * F + f) * width;
+    float ua = 0.f;
+    for (int i = lane; i < width; i += 32) ua = fmaf(to_f(hr[i]), to_f(ur[i]), ua);
+    ua = fmaxf(warp_sum(ua), 0.f);
+    if (lane == 0) act[(size_t)slot * F + f] = from_f<T>(ua * ua);
+    return;
+  }
   const T* gr = w13 + ((size_t)e * 2 * F + f) * width;
   const T* ur = gr + (size_t)F * width;
   float ga = 0.f, ua = 0.f;
@@ -586,7 +597,7 @@ GLLM_EXPORT int gllm_seq_qk_norm_rope_kv_write(const void* qkv, long ld, int nto
                                                const void* qn, const void* kn, float eps, const void* positions,
                                                int rot, double log2_base, void* q_out, void* kc, void* vc,
                                                const void* slots, int ps, int slab, int slab_v, int is_f32,
-                                               void* stream) {
+                                               const void* freqs, float mag, void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 grid(ntok);
@@ -595,11 +606,11 @@ GLLM_EXPORT int gllm_seq_qk_norm_rope_kv_write(const void* qkv, long ld, int nto
                 (qk_norm_rope_kv_write_kernel<bf16_t><<<grid, 256, smem, st>>>(
                     (const bf16_t*)qkv, ld, H, G, D, Dv, (const bf16_t*)qn, (const bf16_t*)kn, eps,
                     (const int*)positions, rot, log2_base, (bf16_t*)q_out, (bf16_t*)kc, (bf16_t*)vc,
-                    (const int*)slots, ps, slab, slab_v)),
+                    (const int*)slots, ps, slab, slab_v, (const double*)freqs, mag)),
                 (qk_norm_rope_kv_write_kernel<float><<<grid, 256, smem, st>>>(
                     (const float*)qkv, ld, H, G, D, Dv, (const float*)qn, (const float*)kn, eps,
                     (const int*)positions, rot, log2_base, (float*)q_out, (float*)kc, (float*)vc, (const int*)slots,
-                    ps, slab, slab_v)));
+                    ps, slab, slab_v, (const double*)freqs, mag)));
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }
@@ -747,19 +758,20 @@ GLLM_EXPORT int gllm_seq_router_select(const void* logits, int ntok, int E, int 
 
 GLLM_EXPORT int gllm_seq_routed_experts(const void* h, long ldh, const void* w13, const void* w2, const void* ids,
                                         const void* wts, int ntok, int top_k, int width, int F, void* act, void* out,
-                                        int is_f32, int n_real, float limit, float alpha, void* stream) {
+                                        int is_f32, int n_real, float limit, float alpha, int ungated,
+                                        void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   dim3 g1(ntok * top_k, (F + 3) / 4), g2(ntok, (width + 3) / 4);
   if (is_f32) {
     moe_gate_up_kernel<float><<<g1, 128, 0, st>>>((const float*)h, ldh, (const float*)w13, (const int*)ids, top_k,
-                                                  width, F, (float*)act, n_real, limit, alpha);
+                                                  width, F, (float*)act, n_real, limit, alpha, ungated);
     moe_down_kernel<float><<<g2, 128, 0, st>>>((const float*)act, (const float*)w2, (const int*)ids,
                                                (const float*)wts, top_k, width, F, (float*)out, (const float*)h, ldh,
                                                n_real);
   } else {
     moe_gate_up_kernel<bf16_t><<<g1, 128, 0, st>>>((const bf16_t*)h, ldh, (const bf16_t*)w13, (const int*)ids, top_k,
-                                                   width, F, (bf16_t*)act, n_real, limit, alpha);
+                                                   width, F, (bf16_t*)act, n_real, limit, alpha, ungated);
     moe_down_kernel<bf16_t><<<g2, 128, 0, st>>>((const bf16_t*)act, (const bf16_t*)w2, (const int*)ids,
                                                 (const float*)wts, top_k, width, F, (bf16_t*)out, (const bf16_t*)h, ldh,
                                                 n_real);

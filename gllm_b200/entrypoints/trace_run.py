@@ -99,7 +99,7 @@ def _require_kernels(model_dir: str):
             cfg = json.load(f)
     except OSError:
         return
-    if cfg.get("architecture") in ("Saritar", "Femolix", "Bevovik"):
+    if cfg.get("architecture") in ("Saritar", "Femolix", "Bevovik", "Notadra"):
         from gllm_b200.ops import lib
         lib.require({"seq", "gemm", "attn", "moe"})
 

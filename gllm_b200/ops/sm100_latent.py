@@ -35,7 +35,7 @@ def _L():
             "gllm_lat_rglru_scan": [P, P, P, P, P, G, P, P, P, P, P, I, I, I, P, I, I, P, I, P],
             "gllm_lat_norm_rope_write": [P, G, G, I, I, P, G, I, I, P, F, P, P, F, P, P, P, I, I, I, I, P],
             "gllm_lat_attention": [P, P, P, I, P, P, I, I, F, I, I, I, P, I, I, I, P],
-            "gllm_lat_grouped_router_select": [P, P, I, I, I, I, I, F, P, P, P],
+            "gllm_lat_grouped_router_select": [P, P, I, I, I, I, I, F, P, P, I, I, I, P],
             "gllm_lat_glu_clamp": [P, G, I, I, P, F, F, I, P],
             "gllm_lat_identity_experts_add": [P, G, P, P, I, I, I, I, P, I, P],
         }
@@ -180,14 +180,15 @@ def latent_attention(q_full, cache, inp, scale, rank, plain: bool = False):
     return out
 
 
-def grouped_router(h, w, correction, top_k, n_groups, keep_groups, scale):
+def grouped_router(h, w, correction, top_k, n_groups, keep_groups, scale, score="softmax", group_top=1, renorm=True):
     t, e = h.shape[0], w.shape[0]
     assert correction is None or (correction.dtype == torch.float32 and correction.is_contiguous())
     logits = sm100_seq.router_logits(h, w)
     wout = torch.empty(t, top_k, dtype=torch.float32, device=h.device)
     ids = torch.empty(t, top_k, dtype=torch.int32, device=h.device)
     check(_L().gllm_lat_grouped_router_select(_p(logits), _p(correction), t, e, int(top_k), int(n_groups),
-                                              int(keep_groups), float(scale), _p(wout), _p(ids), stream_ptr()),
+                                              int(keep_groups), float(scale), _p(wout), _p(ids),
+                                              int(score == "sigmoid"), int(group_top), int(renorm), stream_ptr()),
           "lat_grouped_router_select")
     sm100._count()
     return wout, ids

@@ -66,10 +66,12 @@ def grouped_topk(logits: torch.Tensor, top_k: int, renormalize: bool, n_group: i
 def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: Optional[torch.Tensor],
                   topk_ids: torch.Tensor, expert_map: Optional[torch.Tensor] = None,
                   out: Optional[torch.Tensor] = None, n_valid: Optional[torch.Tensor] = None,
-                  row_dest_fn=None, glu=None) -> Optional[torch.Tensor]:
+                  row_dest_fn=None, glu=None, act: Optional[str] = None) -> Optional[torch.Tensor]:
     """x [T,H]; w13 [E_local, 2I, H] (gate/up rows interleaved per 64); w2 [E_local, H, I]; ids global.
     `glu` = (limit, alpha): the first GEMM's epilogue is the clamped gated form g sigmoid(alpha g) (u + 1) with
     g = min(gate, limit), u = clamp(up, +-limit) instead of silu(gate) * up.
+    `act` = "relu2": ungated experts, w13 is [E_local, I, H] (up rows only, no interleave) and the first GEMM's
+    epilogue squares the positive part of its result.
 
     `n_valid` (device int32 scalar): only the first n_valid rows of x are live (EP receive pool).
     `row_dest_fn(slot_pos, rows)` -> int64 [rows] device table: GEMM2's epilogue then stores every output
@@ -77,7 +79,8 @@ def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: 
     assert x.dtype == _BF16 and x.stride(1) == 1 and w13.is_contiguous() and w2.is_contiguous()
     t, h = x.shape
     e_local, two_i, _ = w13.shape
-    inter = two_i // 2
+    assert act in (None, "relu2") and not (act and glu)
+    inter = two_i if act else two_i // 2
     k = topk_ids.shape[1]
     dev = x.device
     if out is None and row_dest_fn is None:
@@ -95,7 +98,12 @@ def fused_experts(x: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, topk_w: 
     st = stream_ptr()
     check(L.gllm_moe_align_gather(_p(topk_ids), _p(expert_map), t, k, e_local, _p(meta), _p(tile_expert), max_tiles,
                                   _p(slot_pos), _p(x), x.stride(0), _p(xs), h, _p(n_valid), st), "moe_align_gather")
-    if glu is not None:
+    if act is not None:
+        from gllm_b200.ops import sm100_pair
+        sm100_pair._L()      # declares the entry point's signature
+        check(L.gllm_moe_grouped_gemm_act(_p(xs), h, _p(w13), _p(hbuf), inter, max_tiles, inter, h, e_local,
+                                          _p(tile_expert), _p(meta), 1, st), "moe_grouped_gemm1_relu2")
+    elif glu is not None:
         check(L.gllm_moe_grouped_gemm_glu(_p(xs), h, _p(w13), _p(hbuf), inter, max_tiles, two_i, h, e_local,
                                           _p(tile_expert), _p(meta), float(glu[0]), float(glu[1]), st),
               "moe_grouped_gemm1_glu")

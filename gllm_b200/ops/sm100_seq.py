@@ -26,12 +26,12 @@ def _L():
         P, I, G, F = c_void_p, c_int, c_long, c_float
         sigs = {
             "gllm_seq_embed_scale": [P, P, P, I, I, I, F, I, P],
-            "gllm_seq_resid_norm": [P, P, G, P, P, P, P, P, I, I, F, I, I, P],
+            "gllm_seq_resid_norm": [P, P, G, P, P, P, P, P, I, I, F, I, I, F, P],
             "gllm_seq_qk_norm_kv_write": [P, G, I, I, I, I, P, P, F, P, P, P, P, I, I, I, P],
-            "gllm_seq_window_attention": [P, P, P, P, I, P, P, I, I, F, I, I, I, I, I, I, P, P, G, F, I, I, I, I, P],
+            "gllm_seq_window_attention": [P, P, P, P, I, P, P, I, I, F, I, I, I, I, I, I, P, P, G, F, I, I, I, I, F, P],
             "gllm_seq_postnorm": [P, P, G, P, P, I, I, F, F, I, P],
             "gllm_seq_qk_norm_rope_kv_write": [P, G, I, I, I, I, I, P, P, F, P, I, ctypes.c_double, P, P, P, P, I, I, I,
-                                               I, P],
+                                               I, P, F, P],
             "gllm_seq_linear_state": [P, G, P, G, P, G, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, P,
                                       I, I, P, G, P],
             "gllm_seq_key_decay": [P, G, P, F, P, I, I, I, P],
@@ -42,16 +42,16 @@ def _L():
             "gllm_seq_router_logits": [P, G, P, I, I, I, P, I, P],
             "gllm_seq_router_logits_mma": [P, G, P, I, I, I, P, P],
             "gllm_seq_gemm_simt_f32out": [P, G, P, G, P, G, I, I, I, I, P],
-            "gllm_seq_routed_experts": [P, G, P, P, P, P, I, I, I, I, P, P, I, I, F, F, P],
+            "gllm_seq_routed_experts": [P, G, P, P, P, P, I, I, I, I, P, P, I, I, F, F, I, P],
             "gllm_seq_softcap": [P, G, I, I, F, I, P],
             "gllm_seq_conv_silu": [P, G, I, I, I, P, P, I, P, P, P, P, P, I, I, P, P],
             "gllm_seq_selective_scan": [P, P, P, G, P, G, P, P, P, P, P, P, P, I, I, I, I, P, I, I, P],
             "gllm_seq_relu2": [P, P, G, I, P],
-            "gllm_seq_gemm_simt": [P, G, P, G, P, G, I, I, I, I, P],
+            "gllm_seq_gemm_simt": [P, G, P, G, P, G, I, I, I, I, P, P],
             "gllm_attn_decode_win": [P, G, P, P, P, G, P, P, I, I, I, I, I, I, I, F, I, P, P],
             "gllm_attn_prefill_win": [P, G, P, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
-            "gllm_attn_decode_mask": [P, G, P, G, P, P, G, P, P, I, I, I, I, I, I, I, F, I, I, P, F, P],
-            "gllm_attn_prefill_mask": [P, G, P, G, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, F, P],
+            "gllm_attn_decode_mask": [P, G, P, G, P, P, G, P, P, I, I, I, I, I, I, I, F, I, I, P, F, F, P],
+            "gllm_attn_prefill_mask": [P, G, P, G, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, F, F, P],
         }
         for name, args in sigs.items():
             fn = getattr(L, name)
@@ -69,24 +69,26 @@ def _f32(t: torch.Tensor) -> int:
     return 1 if t.dtype == torch.float32 else 0
 
 
-def gemm_simt(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def gemm_simt(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     assert x.dtype == w.dtype and x.stride(1) == 1 and w.stride(1) == 1 and x.shape[1] == w.shape[1]
+    assert bias is None or (bias.dtype == x.dtype and bias.is_contiguous() and bias.shape[0] >= w.shape[0])
     m, k = x.shape
     n = w.shape[0]
     out = torch.empty(m, n, dtype=x.dtype, device=x.device)
     check(_L().gllm_seq_gemm_simt(_p(x), x.stride(0), _p(w), w.stride(0), _p(out), out.stride(0), m, n, k, _f32(x),
-                                  stream_ptr()), "seq_gemm_simt")
+                                  _p(bias), stream_ptr()), "seq_gemm_simt")
     sm100._count()
     return out
 
 
-def linear_any(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+def linear_any(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
     m, k = x.shape
     n = w.shape[0]
     if x.dtype == torch.bfloat16 and k >= _TC_MIN and n >= _TC_MIN and k % 8 == 0 and n % 8 == 0 and \
-            x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0:
-        return sm100.linear(x, w)
-    return gemm_simt(x, w)
+            x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0 and \
+            (bias is None or bias.data_ptr() % 16 == 0):
+        return sm100.linear(x, w, bias)
+    return gemm_simt(x, w, bias)
 
 
 def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
@@ -98,7 +100,7 @@ def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> to
     return out
 
 
-def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None):
+def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None, w_offset=0.0):
     assert x.dtype == torch.float32 and x.is_contiguous()
     t, width = x.shape
     plain = bool(emit_plain) and w_pre is None
@@ -118,7 +120,8 @@ def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_
     if y is None and add is None and w_pre is None and not plain:
         return x if ret_x else None
     check(_L().gllm_seq_resid_norm(_p(x), _p(y), y.stride(0) if y is not None else 0, _p(w_post), _p(post_scale),
-                                   _p(add), _p(w_pre), _p(out), t, width, float(eps), int(plain), is32, stream_ptr()),
+                                   _p(add), _p(w_pre), _p(out), t, width, float(eps), int(plain), is32, float(w_offset),
+                                   stream_ptr()),
           "seq_resid_norm")
     sm100._count()
     return x if ret_x else out
@@ -139,7 +142,7 @@ def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, 
 def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc, positions, scale, num_q_heads,
                      head_dim, window, sink, num_decode_seqs: int = 0, max_q_len: Optional[int] = None,
                      simt: bool = False, chunk: Optional[int] = None, v_dim: Optional[int] = None,
-                     out_scale: float = 1.0, out: Optional[torch.Tensor] = None):
+                     out_scale: float = 1.0, out: Optional[torch.Tensor] = None, softcap: float = 0.0):
     """Masked paged attention: sliding window (None / 0 = full causal) and / or chunk mask, optional per-head softmax
     sink, values `v_dim` wide, result times `out_scale` into `out` (any row stride). bf16 with v_dim == head_dim
     in 64 / 128 / 256 and pages of 8..64 tokens runs on the tensor-core paged-attention kernels
@@ -163,21 +166,23 @@ def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc
             check(L.gllm_attn_decode_mask(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), pages,
                                           _p(block_table), _p(seq_lens), num_decode_seqs, 0, block_table.stride(0),
                                           num_q_heads, hkv, head_dim, ps, float(scale), int(window or 0),
-                                          int(chunk or 0), _p(sink), float(out_scale), st), "attn_decode_mask")
+                                          int(chunk or 0), _p(sink), float(out_scale), float(softcap), st),
+                  "attn_decode_mask")
             sm100._count()
         if nseq > num_decode_seqs:
             check(L.gllm_attn_prefill_mask(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), pages,
                                            _p(block_table), _p(seq_lens), _p(query_start_loc), nseq - num_decode_seqs,
                                            num_decode_seqs, max_q_len, block_table.stride(0), num_q_heads, hkv,
                                            head_dim, ps, float(scale), int(window or 0), int(chunk or 0), _p(sink),
-                                           float(out_scale), st), "attn_prefill_mask")
+                                           float(out_scale), float(softcap), st), "attn_prefill_mask")
             sm100._count()
         return out
     check(_L().gllm_seq_window_attention(_p(q), _p(k_cache), _p(v_cache), _p(block_table), block_table.stride(0),
                                          _p(query_start_loc), _p(positions), t, seq_lens.shape[0], float(scale),
                                          num_q_heads, k_cache.shape[1], head_dim, v_dim, int(window or 0),
                                          int(chunk or 0), _p(sink), _p(out), out.stride(0), float(out_scale), ps, slab,
-                                         v_cache.shape[4], _f32(q), stream_ptr()), "seq_window_attention")
+                                         v_cache.shape[4], _f32(q), float(softcap), stream_ptr()),
+          "seq_window_attention")
     sm100._count()
     return out
 
@@ -229,17 +234,20 @@ def postnorm(x, y, alpha, w, eps, out_dtype):
 
 
 def qk_norm_rope_kv_write(qkv, num_heads, num_kv_heads, dim, v_dim, q_norm_w, k_norm_w, eps, positions, rot_dims,
-                          rot_base, k_cache, v_cache, slots):
+                          rot_base, k_cache, v_cache, slots, freqs=None, mag=1.0):
     import math
     t = qkv.shape[0]
     assert qkv.stride(1) == 1 and k_cache.dtype == qkv.dtype and positions.dim() == 1
+    assert freqs is None or (freqs.dtype == torch.float64 and freqs.is_contiguous() and
+                             freqs.shape[0] == rot_dims // 2)
     q = torch.empty(t, num_heads * dim, dtype=qkv.dtype, device=qkv.device)
     ps = k_cache.shape[3]
     check(_L().gllm_seq_qk_norm_rope_kv_write(_p(qkv), qkv.stride(0), t, num_heads, num_kv_heads, dim, v_dim,
                                               _p(q_norm_w), _p(k_norm_w), float(eps), _p(positions), int(rot_dims),
                                               math.log2(rot_base) if rot_dims > 0 else 0.0, _p(q), _p(k_cache),
                                               _p(v_cache), _p(slots), ps, k_cache.shape[4], v_cache.shape[4],
-                                              _f32(qkv), stream_ptr()), "seq_qk_norm_rope_kv_write")
+                                              _f32(qkv), _p(freqs), float(mag), stream_ptr()),
+          "seq_qk_norm_rope_kv_write")
     sm100._count()
     return q
 
@@ -362,17 +370,19 @@ def router_topk(h, w, top_k, force: Optional[str] = None):
     return wout, ids
 
 
-def routed_experts(h, w13, w2, weights, ids, limit: float = 0.0, alpha: float = 1.702, n_real: Optional[int] = None):
-    """Plain per-slot experts. limit > 0: the clamped gated activation; ids >= n_real: identity experts."""
+def routed_experts(h, w13, w2, weights, ids, limit: float = 0.0, alpha: float = 1.702, n_real: Optional[int] = None,
+                   ungated: bool = False):
+    """Plain per-slot experts. limit > 0: the clamped gated activation; ids >= n_real: identity experts; `ungated`:
+    w13 is [E, F, W] (up rows only) and the activation relu(up h)^2."""
     t, width = h.shape
     n_real = w13.shape[0] if n_real is None else n_real
-    f, k = w13.shape[1] // 2, ids.shape[1]
+    f, k = (w13.shape[1] if ungated else w13.shape[1] // 2), ids.shape[1]
     assert h.stride(1) == 1 and w13.is_contiguous() and w2.is_contiguous() and weights.is_contiguous()
     act = torch.empty(t * k, f, dtype=h.dtype, device=h.device)
     out = torch.empty(t, width, dtype=h.dtype, device=h.device)
     check(_L().gllm_seq_routed_experts(_p(h), h.stride(0), _p(w13), _p(w2), _p(ids), _p(weights), t, k, width, f,
                                        _p(act), _p(out), _f32(h), int(n_real), float(limit), float(alpha),
-                                       stream_ptr()), "seq_routed_experts")
+                                       int(ungated), stream_ptr()), "seq_routed_experts")
     sm100._count(2)
     return out
 
