@@ -57,7 +57,7 @@ def parse():
     ap.add_argument("--layers", type=int, default=0, help="override num_hidden_layers (0 = the model's own); a "
                     "reduced depth is reported in `config.model` and is NOT the named model")
     ap.add_argument("--seed", type=int, default=0)
-    ap.add_argument("--design", default=None, choices=["saritar", "femolix", "bevovik"],
+    ap.add_argument("--design", default=None, choices=["saritar", "femolix", "bevovik", "notadra"],
                     help="side benchmark: prefill / decode throughput and kernel rooflines of that design beside "
                          "the closest existing decoder at equal size (benchmarks/design_bench.py); 1 GPU")
     ap.add_argument("--async-schedule", action=argparse.BooleanOptionalAction, default=True,

@@ -1,12 +1,15 @@
 """Prefill / decode throughput of a layer-list design beside the closest existing decoder at matched width, depth and
 (roughly) parameter count, through the public `LLM.generate` API with random weights, plus the device time of each
 new kernel against its roofline and against the like kernel of the existing path. Invoked as
-`python bench.py --design saritar|femolix|bevovik` (the default benchmark is untouched).
+`python bench.py --design saritar|femolix|bevovik|notadra` (the default benchmark is untouched).
 
   saritar  beside Qwen3 (GQA attention with q/k norm + gated MLP)
   femolix  beside Qwen3-MoE (rotary GQA attention with q/k norm + routed gated experts)
   bevovik  beside DeepSeek-V3 (latent attention with YaRN rotary + group-limited routing with a correction bias and a
            shared expert)
+  notadra  beside Qwen3-MoE (rotary GQA attention + routed experts; the design adds biases, YaRN frequencies, capped
+           scores, a unit sink, layers on shared key / value pages, sigmoid group-limited routing, ungated
+           squared-ReLU experts and a hashed pair embedding)
 
 Prints ONE JSON line: {"design": ..., "sizes": [{"width", ..., "<design>": {...}, "<closest>": {...}}], "kernels": [...]}
 """
@@ -82,6 +85,27 @@ def _bevovik_cfg(width, n_quads, vocab, experts=14, identity=2, top=2):
                             "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}, "mlp": ff}
     return {"architecture": "Bevovik", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "layers": [rg, gl, la, rg] * n_quads}
+
+
+def _notadra_cfg(width, layers, vocab, experts=16, top=2):
+    """Rotary attention layers of which every second one reads the keys and values of the layer before it, every
+    layer with a routed feed-forward: 16 ungated experts of 1.5 x width (the parameter count of a gated expert of
+    width) in 4 groups of which 2 are kept."""
+    heads = width // 128
+    kv = max(heads // 4, 1)
+    ff = {"kind": "moe", "expert": {"ff": 3 * width // 2},
+          "router": {"experts": experts, "top": top, "groups": {"count": 4, "keep": 2}}}
+
+    def att(src):
+        m = {"dim": 128, "heads": heads, "kv_heads": kv, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+             "rot": {"base": 1e6, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+        if src is not None:
+            m["kv_from"] = src
+        return {"type": "attention", "mixer": m, "mlp": ff}
+
+    return {"architecture": "Notadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}},
+            "layers": [att(i - 1 if i % 2 else None) for i in range(layers)]}
 
 
 def _deepseek_cfg(width, layers, vocab, experts=16, top=2):
@@ -358,6 +382,8 @@ def run(args):
         return run_femolix(args, peaks)
     if getattr(args, "design", "saritar") == "bevovik":
         return run_bevovik(args, peaks)
+    if getattr(args, "design", "saritar") == "notadra":
+        return run_notadra(args, peaks)
     vocab = 32000
     kernels = _kernels(peaks)
     sizes = []
@@ -547,6 +573,143 @@ def run_bevovik(args, peaks):
                       "bevovik": _throughput(b_cfg, vocab, args.warmup, args.steps),
                       "deepseek_v3": _throughput(d_cfg, vocab, args.warmup, args.steps)})
     line = {"design": "bevovik", "dtype": "bf16", "data": "synthetic", "warmup": args.warmup, "steps": args.steps,
+            "timing": "wall clock around LLM.generate with synchronize (sizes); CUDA events, L2 flushed (kernels)",
+            "peaks": peaks, "sizes": sizes, "kernels": kernels}
+    print(json.dumps(line))
+    return line
+
+
+def _kernels_notadra(peaks):
+    """Device time of the kernels this design added or extended, at layer-like sizes, each beside the like kernel of
+    the existing path (Qwen3-MoE's rotary write, paged attention, router and gated experts). Bytes are the
+    algorithmic minimum."""
+    from gllm_b200.ops import ref, sm100, sm100_latent as Lt, sm100_moe, sm100_pair as Pr, sm100_seq as S
+    dev, bf = "cuda", torch.bfloat16
+    hbm = float(peaks.get("hbm_gbs", 6650.0))
+    out = []
+
+    def row(name, ms, nbytes, like=None, flops=None):
+        r = {"kernel": name, "ms": round(ms, 4), "gbs": round(nbytes / ms / 1e6, 1),
+             "frac_hbm": round(nbytes / ms / 1e6 / hbm, 3)}
+        if flops:
+            r["tflops"] = round(flops / ms / 1e9, 2)
+        if like:
+            r["like"] = like
+        out.append(r)
+
+    T, W, V = 8192, 4096, 32000
+    ids = torch.randint(0, V, (T,), dtype=torch.int32, device=dev)
+    table, pair = torch.randn(V, W, device=dev).to(bf), torch.randn(65522, W, device=dev).to(bf)
+    qsl4 = torch.tensor([0, 2048, 4096, 6144, 8192], dtype=torch.int32, device=dev)
+    pos4 = torch.arange(2048, dtype=torch.int32, device=dev).repeat(4)
+    st = torch.zeros(8, dtype=torch.int32, device=dev)
+    rs = torch.arange(4, dtype=torch.int32, device=dev)
+    row("pair_embed (token row + hashed pair row -> fp32 stream) 8192 x 4096",
+        _time(lambda: Pr.embedding_pair_hash(ids, table, pair, 1000003, 31, 65521, pos4, st, rs, qsl4)),
+        T * W * (2 + 2 + 4))
+    row("embedding (existing: one row, bf16 out)", _time(lambda: sm100.embedding(ids, table)), T * W * (2 + 2),
+        like="pair_embed")
+    x = torch.randn(T, W, device=dev)
+    y, w1 = torch.randn(T, W, device=dev).to(bf), torch.zeros(W, device=dev).to(bf)
+    row("resid_norm with gain 1 + w (post-norm + add + pre-norm, fp32 stream in/out, bf16 in/out)",
+        _time(lambda: S.resid_norm(x, y, w1, None, w1, 1e-5, bf, False, None, 1.0)), T * W * (4 + 4 + 2 + 2))
+    res = torch.randn(T, W, device=dev).to(bf)
+    row("rmsnorm + residual (existing bf16 path)", _time(lambda: sm100.rmsnorm(y, w1, 1e-5, res)),
+        T * W * (2 + 2 + 2 + 2), like="resid_norm")
+    H, G, D, ps = 32, 8, 128, 16
+    fr, mag = ref.pair_rotary_frequencies(64, 1e6, {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0},
+                                          dtype=torch.float64)
+    fr = fr.to(dev)
+    sink = torch.zeros(H, device=dev)
+    for label, qlens, ctx in (("prefill 4 x 2048", [2048] * 4, 0), ("decode 256 x 1 at 2048", [1] * 256, 2047)):
+        Tt, B = sum(qlens), len(qlens)
+        qsl = torch.tensor([0] + torch.tensor(qlens).cumsum(0).tolist(), dtype=torch.int32, device=dev)
+        sl = torch.tensor([q + ctx for q in qlens], dtype=torch.int32, device=dev)
+        npp = (max(qlens) + ctx + ps - 1) // ps
+        bt = torch.arange(B * npp, dtype=torch.int32, device=dev).reshape(B, npp)
+        kshape = ref.kv_cache_shape(B * npp + 1, G, D, ps)
+        kc, vc = torch.randn(kshape, device=dev).to(bf), torch.randn(kshape, device=dev).to(bf)
+        pos = torch.cat([torch.arange(ctx, ctx + q) for q in qlens]).to(torch.int32).to(dev)
+        seqi = torch.cat([torch.full((q,), i) for i, q in enumerate(qlens)]).to(dev)
+        slots = (bt[seqi, (pos // ps).long()] * ps + pos % ps).to(torch.int32)
+        qkv = torch.randn(Tt, (H + 2 * G) * D, device=dev).to(bf)
+        ms = _time(lambda: S.qk_norm_rope_kv_write(qkv, H, G, D, D, None, None, 1e-5, pos, 64, 1e6, kc, vc, slots, fr,
+                                                   mag))
+        row("rotary write (frequency table, first 64 of 128 entries, cache write) " + label, ms,
+            Tt * (H + 2 * G) * D * 2 * 2)
+        ms = _time(lambda: S.qk_norm_rope_kv_write(qkv[:, :H * D], H, 0, D, D, None, None, 1e-5, pos, 64, 1e6, kc, vc,
+                                                   slots, fr, mag))
+        row("rotary write, queries only (layer on shared pages) " + label, ms, Tt * H * D * 2 * 2)
+        cs = torch.randn(8192, D, device=dev)
+        qq = qkv[:, :H * D].unflatten(1, (H, D))
+        kk = qkv[:, H * D:(H + G) * D].unflatten(1, (G, D))
+        vv = qkv[:, (H + G) * D:].unflatten(1, (G, D))
+        ms2 = _time(lambda: sm100.rope_kv_write(qq, kk, vv, pos, cs, D, True, None, None, 1e-5, kc, vc, slots))
+        row("rope_kv_write (existing: table rotary + cache write) " + label, ms2, Tt * (H + 2 * G) * D * 2 * 2,
+            like="rotary write")
+        q = torch.randn(Tt, H * D, device=dev).to(bf)
+        keys = sum(p + 1 for ql in qlens for p in range(ctx, ctx + ql))
+        nd = B if qlens[0] == 1 else 0
+        ms = _time(lambda: S.window_attention(q, kc, vc, bt, sl, qsl, pos, D ** -0.5, H, D, None, sink,
+                                              num_decode_seqs=nd, max_q_len=max(qlens), v_dim=D, softcap=50.0),
+                   iters=5)
+        r = {"kernel": "capped sink attention (tensor-core paged kernel) " + label, "ms": round(ms, 4),
+             "tflops": round(4.0 * keys * H * D / ms / 1e9, 2)}
+        ms2 = _time(lambda: sm100.paged_attention(q, kc, vc, bt, sl, qsl, D ** -0.5, H, D, nd, B, max(qlens),
+                                                  max(qlens) + ctx), iters=3)
+        r["like"] = {"kernel": "paged_attention (existing, no cap, no sink)", "ms": round(ms2, 4),
+                     "tflops": round(4.0 * keys * H * D / ms2 / 1e9, 2)}
+        out.append(r)
+    T2, E, top = 8192, 16, 2
+    hh = torch.randn(T2, W, device=dev).to(bf)
+    wr, corr = (torch.randn(E, W, device=dev) * W ** -0.5).to(bf), torch.randn(E, device=dev) * 0.1
+    row("grouped_router (fp32 logits + sigmoid + correction + top-2-sum group limit + top-2) 8192 x 4096 x 16",
+        _time(lambda: Lt.grouped_router(hh, wr, corr, top, 4, 2, 1.0, "sigmoid", 2, False)), T2 * W * 2 + E * W * 2)
+    row("router GEMM + topk_softmax (existing)",
+        _time(lambda: sm100_moe.topk_softmax(sm100.linear(hh, wr), top, True)), T2 * W * 2 + E * W * 2,
+        like="grouped_router")
+    hd = hh[:64]
+    row("grouped_router decode, 64 x 4096 x 16",
+        _time(lambda: Lt.grouped_router(hd, wr, corr, top, 4, 2, 1.0, "sigmoid", 2, False)), E * W * 2 + 64 * W * 2)
+    row("router GEMM + topk_softmax decode (existing)",
+        _time(lambda: sm100_moe.topk_softmax(sm100.linear(hd, wr), top, True)), E * W * 2 + 64 * W * 2,
+        like="grouped_router decode")
+    F = 3072
+    wu = (torch.randn(E, F, W, device=dev) * W ** -0.5).to(bf)
+    wd = (torch.randn(E, W, F, device=dev) * F ** -0.5).to(bf)
+    wts, idx = Lt.grouped_router(hh, wr, corr, top, 4, 2, 1.0, "sigmoid", 2, False)
+    row("routed_relu2_experts (grouped tcgen05 GEMMs, squared-ReLU epilogue, ff 3072)",
+        _time(lambda: Pr.routed_relu2_experts(hh, wu, wd, wts, idx, True), iters=5),
+        wu.numel() * 2 + wd.numel() * 2 + T2 * W * 2 * 2, flops=4.0 * T2 * top * W * F)
+    Fg = 2048
+    w13 = (torch.randn(E, 2 * Fg, W, device=dev) * W ** -0.5).to(bf)
+    w2 = (torch.randn(E, W, Fg, device=dev) * Fg ** -0.5).to(bf)
+    row("fused_experts (existing: SiLU-gate epilogue, ff 2048: the same weights' size)",
+        _time(lambda: sm100_moe.fused_experts(hh, w13, w2, wts, idx), iters=5),
+        w13.numel() * 2 + w2.numel() * 2 + T2 * W * 2 * 2, like="routed_relu2_experts",
+        flops=6.0 * T2 * top * W * Fg)
+    hd64 = hh[:64]
+    wt64, id64 = wts[:64].contiguous(), idx[:64].contiguous()
+    row("routed_relu2_experts decode, 64 tokens", _time(lambda: Pr.routed_relu2_experts(hd64, wu, wd, wt64, id64, True)),
+        wu.numel() * 2 + wd.numel() * 2, flops=4.0 * 64 * top * W * F)
+    row("fused_experts decode, 64 tokens (existing)", _time(lambda: sm100_moe.fused_experts(hd64, w13, w2, wt64, id64)),
+        w13.numel() * 2 + w2.numel() * 2, like="routed_relu2_experts decode", flops=6.0 * 64 * top * W * Fg)
+    z = torch.randn(256, V, device=dev).to(bf)
+    row("scale_rows (logits * scale in place) 256 x 32000", _time(lambda: Pr.scale_rows(z, 0.5)), 256 * V * 2 * 2)
+    return out
+
+
+def run_notadra(args, peaks):
+    vocab = 32000
+    kernels = _kernels_notadra(peaks)
+    sizes = []
+    for width, layers in ((1024, 8), (2048, 8), (4096, 4)):
+        n_cfg = _notadra_cfg(width, layers, vocab)
+        q_cfg = _qwen3_moe_cfg(width, layers, vocab)
+        sizes.append({"width": width, "layers": layers,
+                      "notadra": _throughput(n_cfg, vocab, args.warmup, args.steps),
+                      "qwen3_moe": _throughput(q_cfg, vocab, args.warmup, args.steps)})
+    line = {"design": "notadra", "dtype": "bf16", "data": "synthetic", "warmup": args.warmup, "steps": args.steps,
             "timing": "wall clock around LLM.generate with synchronize (sizes); CUDA events, L2 flushed (kernels)",
             "peaks": peaks, "sizes": sizes, "kernels": kernels}
     print(json.dumps(line))
