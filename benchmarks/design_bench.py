@@ -653,7 +653,8 @@ def _kernels_notadra(peaks):
         ms = _time(lambda: S.window_attention(q, kc, vc, bt, sl, qsl, pos, D ** -0.5, H, D, None, sink,
                                               num_decode_seqs=nd, max_q_len=max(qlens), v_dim=D, softcap=50.0),
                    iters=5)
-        r = {"kernel": "capped sink attention (tensor-core paged kernel) " + label, "ms": round(ms, 4),
+        r = {"kernel": "capped sink attention (tcgen05 prefill kernel for portions, tensor-core paged kernel for "
+                       "decode rows) " + label, "ms": round(ms, 4),
              "tflops": round(4.0 * keys * H * D / ms / 1e9, 2)}
         ms2 = _time(lambda: sm100.paged_attention(q, kc, vc, bt, sl, qsl, D ** -0.5, H, D, nd, B, max(qlens),
                                                   max(qlens) + ctx), iters=3)

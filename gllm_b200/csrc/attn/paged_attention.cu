@@ -49,9 +49,6 @@ struct AttnParams {
   float cap_log2, scale_over_cap;
 };
 
-// tanh from exp and a division (this file is built with approximate intrinsics: the hardware tanh approximation
-// would cost the scores three more bits than this form does); +-1 at the ends, |error| ~ 1e-7 near 0
-__device__ __forceinline__ float tanh_exp(float x) { return 1.0f - __fdividef(2.0f, __expf(2.0f * x) + 1.0f); }
 
 template <int D>
 struct AttnSmem {

@@ -43,6 +43,11 @@ struct TcAttnParams {
   const int32_t* q_start;
   int max_blocks, Hq, Hkv, G, GP, page_size, seq_offset;
   float scale_log2;
+  // score cap (kernel template CAP): a scaled score s becomes cap * tanh(s / cap); cap_log2 = cap * log2(e),
+  // scale_over_cap = scale / cap. sink: one extra logit per query head in the softmax denominator that carries no
+  // value (null = none)
+  float cap_log2, scale_over_cap;
+  const float* sink;
   uint32_t v_lbo16, v_sbo16, v_kadv16, v_split_n;   // MN-major V descriptor fields (16-byte units)
 };
 
@@ -93,7 +98,7 @@ __device__ __forceinline__ uint32_t a_tile_off(int row, int c) {
   return (c >> 3) * (kTcRows * 128) + row * 128 + (((c & 7) ^ (row & 7)) << 4);
 }
 
-template <int D, int KV>
+template <int D, int KV, bool CAP>
 __global__ void __launch_bounds__(kTcThreads, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_v,
                        const TcAttnParams p) {
@@ -274,7 +279,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
           for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[e]));
         }
       }
-      const float m_new = fmaxf(m_run, mx * p.scale_log2);
+      // the cap is increasing in the score: the capped maximum is the cap of the raw maximum
+      const float mx_s = !CAP ? mx * p.scale_log2
+                              : (mx == -INFINITY ? -INFINITY : p.cap_log2 * tanh_exp(mx * p.scale_over_cap));
+      const float m_new = fmaxf(m_run, mx_s);
       const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
       const float alpha = exp2f(m_run - m_use);
       m_run = m_new;
@@ -289,7 +297,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
         float f[32];
 #pragma unroll
         for (int e = 0; e < 32; ++e) {
-          float x = exp2f(fmaf(__uint_as_float(v[e]), p.scale_log2, -m_use));
+          float x = CAP ? exp2f(fmaf(p.cap_log2, tanh_exp(__uint_as_float(v[e]) * p.scale_over_cap), -m_use))
+                        : exp2f(fmaf(__uint_as_float(v[e]), p.scale_log2, -m_use));
           if (need_mask && key0 + c + e > lim) x = 0.f;
           f[e] = x;
           sum += x;
@@ -332,6 +341,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_k, const __grid_
     const int lt = n_tiles - 1;
     mbar_wait(&pv_done[lt & 1], (lt >> 1) & 1);
     tc_fence_after();
+    if (p.sink != nullptr && row_ok && m_run > -INFINITY) l_run += exp2f(p.sink[head] * 1.4426950408889634f - m_run);
     const float inv = l_run > 0.f ? 1.f / l_run : 0.f;
     __nv_bfloat16* op = p.out + (static_cast<size_t>(q_begin + tok) * p.Hq + head) * D;
     const uint32_t t_o = tmem_o + lane_base;
@@ -391,19 +401,19 @@ static int get_kv_slab_tmap(const void* base, int64_t num_pages, int Hkv, int D,
   return 0;
 }
 
-template <int D, int KV>
+template <int D, int KV, bool CAP = false>
 static int launch_prefill_tc(const CUtensorMap& tk, const CUtensorMap& tv, const TcAttnParams& p, int num_seqs,
                              int max_q_len, cudaStream_t st) {
   using SM = TcSmem<D, KV>;
   static PerDeviceOnce configured;
   if (configured.need()) {
-    CUDA_CHECK_RET(cudaFuncSetAttribute(attn_prefill_tc_kernel<D, KV>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    CUDA_CHECK_RET(cudaFuncSetAttribute(attn_prefill_tc_kernel<D, KV, CAP>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         SM::kBytes));
     configured.done();
   }
   const int toks_per_tile = kTcRows / p.GP;
   dim3 grid((max_q_len + toks_per_tile - 1) / toks_per_tile, num_seqs, p.Hkv * (p.G / p.GP));
-  attn_prefill_tc_kernel<D, KV><<<grid, kTcThreads, SM::kBytes, st>>>(tk, tv, p);
+  attn_prefill_tc_kernel<D, KV, CAP><<<grid, kTcThreads, SM::kBytes, st>>>(tk, tv, p);
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }
@@ -415,11 +425,11 @@ using namespace b200;
 // Same contract as gllm_attn_prefill (paged_attention.cu). Returns 2 when the shape is outside this kernel's
 // envelope (head_dim 64 / 128, page_size dividing the KV tile) — the caller then uses the mma.sync kernel.
 // kv_tile: 64 or 128 keys per pipeline stage.
-GLLM_EXPORT int gllm_attn_prefill_tc(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
-                                     int64_t num_pages, const void* block_table, const void* seq_lens,
-                                     const void* q_start, int num_seqs, int seq_offset, int max_q_len,
-                                     int max_blocks, int Hq, int Hkv, int D, int page_size, float scale, int kv_tile,
-                                     void* stream) {
+static int attn_prefill_tc_impl(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
+                                int64_t num_pages, const void* block_table, const void* seq_lens,
+                                const void* q_start, int num_seqs, int seq_offset, int max_q_len,
+                                int max_blocks, int Hq, int Hkv, int D, int page_size, float scale, int kv_tile,
+                                const void* sink, float softcap, void* stream) {
   if (num_seqs <= 0 || max_q_len <= 0) return 0;
   if ((D != 64 && D != 128) || (kv_tile != 64 && kv_tile != 128) || page_size < 8 || kv_tile % page_size != 0 ||
       Hq % Hkv != 0)
@@ -439,6 +449,9 @@ GLLM_EXPORT int gllm_attn_prefill_tc(const void* q, int64_t q_ts, void* out, con
     if (p.G % d == 0 && kTcRows % d == 0) { p.GP = d; break; }
   p.page_size = page_size; p.seq_offset = seq_offset;
   p.scale_log2 = scale * 1.4426950408889634f;
+  p.cap_log2 = softcap > 0.f ? softcap * 1.4426950408889634f : 0.f;
+  p.scale_over_cap = softcap > 0.f ? scale / softcap : 0.f;
+  p.sink = reinterpret_cast<const float*>(sink);
   // MN-major V operand (see the header comment); overridable for bring-up
   p.v_lbo16 = static_cast<uint32_t>(kv_tile * 128) >> 4;
   p.v_sbo16 = 1024 >> 4;
@@ -451,10 +464,40 @@ GLLM_EXPORT int gllm_attn_prefill_tc(const void* q, int64_t q_ts, void* out, con
     }
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (softcap > 0.f) {
+    if (D == 128) {
+      return kv_tile == 128 ? launch_prefill_tc<128, 128, true>(tk, tv, p, num_seqs, max_q_len, st)
+                            : launch_prefill_tc<128, 64, true>(tk, tv, p, num_seqs, max_q_len, st);
+    }
+    return kv_tile == 128 ? launch_prefill_tc<64, 128, true>(tk, tv, p, num_seqs, max_q_len, st)
+                          : launch_prefill_tc<64, 64, true>(tk, tv, p, num_seqs, max_q_len, st);
+  }
   if (D == 128) {
     return kv_tile == 128 ? launch_prefill_tc<128, 128>(tk, tv, p, num_seqs, max_q_len, st)
                           : launch_prefill_tc<128, 64>(tk, tv, p, num_seqs, max_q_len, st);
   }
   return kv_tile == 128 ? launch_prefill_tc<64, 128>(tk, tv, p, num_seqs, max_q_len, st)
                         : launch_prefill_tc<64, 64>(tk, tv, p, num_seqs, max_q_len, st);
+}
+
+GLLM_EXPORT int gllm_attn_prefill_tc(const void* q, int64_t q_ts, void* out, const void* k_cache, const void* v_cache,
+                                     int64_t num_pages, const void* block_table, const void* seq_lens,
+                                     const void* q_start, int num_seqs, int seq_offset, int max_q_len,
+                                     int max_blocks, int Hq, int Hkv, int D, int page_size, float scale, int kv_tile,
+                                     void* stream) {
+  return attn_prefill_tc_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, q_start, num_seqs,
+                              seq_offset, max_q_len, max_blocks, Hq, Hkv, D, page_size, scale, kv_tile, nullptr, 0.f,
+                              stream);
+}
+
+// the same full-causal attention with a per-head softmax sink (null = none) and a tanh cap on the scaled scores
+// (0 = none); output rows are dense ([tokens, Hq * D])
+GLLM_EXPORT int gllm_attn_prefill_tc_cap(const void* q, int64_t q_ts, void* out, const void* k_cache,
+                                         const void* v_cache, int64_t num_pages, const void* block_table,
+                                         const void* seq_lens, const void* q_start, int num_seqs, int seq_offset,
+                                         int max_q_len, int max_blocks, int Hq, int Hkv, int D, int page_size,
+                                         float scale, int kv_tile, const void* sink, float softcap, void* stream) {
+  return attn_prefill_tc_impl(q, q_ts, out, k_cache, v_cache, num_pages, block_table, seq_lens, q_start, num_seqs,
+                              seq_offset, max_q_len, max_blocks, Hq, Hkv, D, page_size, scale, kv_tile, sink, softcap,
+                              stream);
 }

@@ -50,6 +50,7 @@ def _L():
             "gllm_seq_gemm_simt": [P, G, P, G, P, G, I, I, I, I, P, P],
             "gllm_attn_decode_win": [P, G, P, P, P, G, P, P, I, I, I, I, I, I, I, F, I, P, P],
             "gllm_attn_prefill_win": [P, G, P, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, P, P],
+            "gllm_attn_prefill_tc_cap": [P, G, P, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, P, F, P],
             "gllm_attn_decode_mask": [P, G, P, G, P, P, G, P, P, I, I, I, I, I, I, I, F, I, I, P, F, F, P],
             "gllm_attn_prefill_mask": [P, G, P, G, P, P, G, P, P, P, I, I, I, I, I, I, I, I, F, I, I, P, F, F, P],
         }
@@ -169,7 +170,19 @@ def window_attention(q, k_cache, v_cache, block_table, seq_lens, query_start_loc
                                           int(chunk or 0), _p(sink), float(out_scale), float(softcap), st),
                   "attn_decode_mask")
             sm100._count()
-        if nseq > num_decode_seqs:
+        rest = nseq > num_decode_seqs
+        if rest and not window and not chunk and sm100.ATTN_TC and out_scale == 1.0 and \
+                out.stride(0) == num_q_heads * head_dim and head_dim in (64, 128) and sm100.ATTN_TC_KV % ps == 0:
+            # full causal (cap and sink only): the tcgen05 prefill kernel
+            rc = L.gllm_attn_prefill_tc_cap(_p(q), q.stride(0), _p(out), _p(k_cache), _p(v_cache), pages,
+                                            _p(block_table), _p(seq_lens), _p(query_start_loc), nseq - num_decode_seqs,
+                                            num_decode_seqs, max_q_len, block_table.stride(0), num_q_heads, hkv,
+                                            head_dim, ps, float(scale), sm100.ATTN_TC_KV, _p(sink), float(softcap), st)
+            if rc != 2:                     # 2 = shape outside that kernel's envelope -> the mma.sync kernel
+                check(rc, "attn_prefill_tc_cap")
+                sm100._count()
+                rest = False
+        if rest:
             check(L.gllm_attn_prefill_mask(_p(q), q.stride(0), _p(out), out.stride(0), _p(k_cache), _p(v_cache), pages,
                                            _p(block_table), _p(seq_lens), _p(query_start_loc), nseq - num_decode_seqs,
                                            num_decode_seqs, max_q_len, block_table.stride(0), num_q_heads, hkv,

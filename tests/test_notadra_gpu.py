@@ -171,7 +171,8 @@ def test_rotary_write_and_capped_sink_attention(dt, tol, heads, kvh, dim, vdim, 
     torch.manual_seed(5)
     for qlens, ctx, ps, cap, sc in (([1, 1, 9, 3], [35, 16, 0, 2], 16, 3.0, YARN2),
                                     ([1, 70, 33], [200, 0, 31], 16, 30.0, None),
-                                    ([1, 1, 1], [0, 77, 15], 8, 1.5, YARN2)):
+                                    ([1, 1, 1], [0, 77, 15], 8, 1.5, YARN2),
+                                    ([1, 40, 150], [5, 0, 130], 16, 0.0, None)):          # sink without a cap
         got, want = _attn_case(dt, heads, kvh, dim, vdim, rot, qlens, ctx, ps, cap, sc)
         for g, w, name in zip(got, want, ("queries", "keys", "values", "attention", "attention (plain)")):
             assert close(g, w, tol), (name, qlens)
