@@ -103,7 +103,7 @@ def _notadra_cfg(width, layers, vocab, experts=16, top=2):
             m["kv_from"] = src
         return {"type": "attention", "mixer": m, "mlp": ff}
 
-    return {"architecture": "Notadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.5,
+    return {"architecture": "Notadra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "logit_scale": 0.75,
             "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}},
             "layers": [att(i - 1 if i % 2 else None) for i in range(layers)]}
 

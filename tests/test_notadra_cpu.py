@@ -253,7 +253,7 @@ def test_router_corner_cases():
 
 def test_feed_forward_alone():
     g = torch.Generator().manual_seed(7)
-    for mlp, width in ((U.moe(), 20), (U.moe(experts=12, top=3, ff=5, groups=(2, 1)), 12),
+    for mlp, width in ((U.moe(), 20), (U.moe(experts=10, top=3, ff=5, groups=(2, 1)), 12),
                        (U.moe(experts=3, top=3, ff=7, groups=None), 9), (U.moe(experts=4, top=1, ff=2, groups=(4, 3)), 8)):
         cfg = U.make_config([U.attn(mlp=mlp)], width=width)
         w = U.random_weights(cfg, 7)
