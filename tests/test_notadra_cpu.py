@@ -27,7 +27,8 @@ CONFIGS = {
                                    mlp=U.moe(experts=5, top=2, groups=None)),
                             U.attn(kv_from=0, softcap=50.0, scale=0.2, mlp=None)]),
     "own_only": U.make_config([U.attn(heads=3, kv_heads=3, dim=4, vdim=4, rot_dims=2, scaling=None, mlp=U.moe()),
-                               U.attn(heads=6, kv_heads=2, dim=10, vdim=3, rot_dims=10, mlp=U.moe(top=4, groups=(2, 2)))],
+                               U.attn(heads=6, kv_heads=2, dim=10, vdim=3, rot_dims=10,
+                                      mlp=U.moe(top=4, groups=(2, 2)))],
                               bigram=(7, 1000003, 999983), logit_scale=1.0),
     # sizes of one, values that other models make equal or 1
     "ones": U.make_config([U.attn(heads=1, kv_heads=1, dim=2, vdim=1, rot_dims=2, scale=1.0, softcap=1.0,
@@ -90,8 +91,8 @@ def test_pair_embedding_rows_and_carried_token():
         plan = [((0, 4), (0, 1)), ((4, 5), (1, 2)), ((5, 9), (2, 5))]
         got0, got1 = [], []
         for (a0, b0), (a1, b1) in plan:
-            inp = _Inp(s0[a0:b0] + s1[a1:b1], list(range(a0, b0)) + list(range(a1, b1)), [0, b0 - a0, b0 - a0 + b1 - a1],
-                       [2, 0])
+            inp = _Inp(s0[a0:b0] + s1[a1:b1], list(range(a0, b0)) + list(range(a1, b1)),
+                       [0, b0 - a0, b0 - a0 + b1 - a1], [2, 0])
             x = Fn.embedding_pair_hash(inp, wt["embed"], wt["bigram"], a, b, buckets, state)
             got0.append(x[:b0 - a0])
             got1.append(x[b0 - a0:])
@@ -226,8 +227,8 @@ def test_router_corner_cases():
         n = wr.shape[0]
         r = {"experts": n, "top": top, "groups": {"count": cnt, "keep": keep}}
         ids, ws = oracle.route(torch.eye(wr.shape[1], dtype=torch.float64)[:1], r, wt, "r.")
-        gw, gi = ref.grouped_router(torch.eye(wr.shape[1])[:1], wr, torch.tensor(corr), top, cnt, keep, 1.0, "sigmoid", 2,
-                                    False)
+        gw, gi = ref.grouped_router(torch.eye(wr.shape[1])[:1], wr, torch.tensor(corr), top, cnt, keep, 1.0,
+                                    "sigmoid", 2, False)
         assert gi[0].tolist() == ids[0], (gi, ids)
         assert np.allclose(gw[0].numpy(), ws[0], atol=1e-6)
         return ids[0], ws[0]
@@ -254,7 +255,8 @@ def test_router_corner_cases():
 def test_feed_forward_alone():
     g = torch.Generator().manual_seed(7)
     for mlp, width in ((U.moe(), 20), (U.moe(experts=10, top=3, ff=5, groups=(2, 1)), 12),
-                       (U.moe(experts=3, top=3, ff=7, groups=None), 9), (U.moe(experts=4, top=1, ff=2, groups=(4, 3)), 8)):
+                       (U.moe(experts=3, top=3, ff=7, groups=None), 9),
+                       (U.moe(experts=4, top=1, ff=2, groups=(4, 3)), 8)):
         cfg = U.make_config([U.attn(mlp=mlp)], width=width)
         w = U.random_weights(cfg, 7)
         f = U.build_ff(mlp, w, width)

@@ -103,7 +103,8 @@ def test_pair_embedding_on_the_device(dt):
     for buckets, a, b in ((11, 7, 3), (1, 5, 9), (499, 2 ** 31 - 1, 2 ** 31 - 19), (4, 0, 1)):
         table = torch.randn(vocab, width, device=DEV).to(dt)
         pair = torch.randn(buckets + 1, width, device=DEV).to(dt)
-        for qlens, ctx in (([1, 1, 5, 9], [4, 0, 0, 17]), ([7], [0]), ([1, 1, 1], [3, 9, 0]), ([2, 2, 64], [5, 0, 100])):
+        for qlens, ctx in (([1, 1, 5, 9], [4, 0, 0, 17]), ([7], [0]), ([1, 1, 1], [3, 9, 0]),
+                           ([2, 2, 64], [5, 0, 100])):
             bt = _batch(qlens, ctx, 4, 2 + len(qlens) * max((c + q + 3) // 4 for c, q in zip(ctx, qlens)))
             T = int(bt.query_start_loc[-1])
             ids = torch.randint(0, vocab, (T,), dtype=torch.int32, device=DEV)
@@ -163,6 +164,7 @@ YARN2 = {"factor": 8.0, "original": 64, "fast": 16.0, "slow": 1.0}
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 5e-5), (torch.bfloat16, 2e-2)])
 @pytest.mark.parametrize("heads,kvh,dim,vdim,rot", [(4, 2, 8, 6, 4), (1, 1, 2, 1, 2), (8, 4, 128, 80, 32),
                                                     (8, 2, 128, 128, 64), (4, 4, 64, 64, 64), (6, 3, 256, 256, 32),
+                                                    (6, 2, 64, 64, 16), (3, 1, 128, 128, 128),
                                                     (5, 5, 24, 40, 24)])
 def test_rotary_write_and_capped_sink_attention(dt, tol, heads, kvh, dim, vdim, rot):
     """Sizes that take the plain kernel (values narrower than keys, fp32) and sizes that take the tensor-core
