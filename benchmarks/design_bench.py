@@ -695,8 +695,6 @@ def _kernels_notadra(peaks):
         wu.numel() * 2 + wd.numel() * 2, flops=4.0 * 64 * top * W * F)
     row("fused_experts decode, 64 tokens (existing)", _time(lambda: sm100_moe.fused_experts(hd64, w13, w2, wt64, id64)),
         w13.numel() * 2 + w2.numel() * 2, like="routed_relu2_experts decode", flops=6.0 * 64 * top * W * Fg)
-    z = torch.randn(256, V, device=dev).to(bf)
-    row("scale_rows (logits * scale in place) 256 x 32000", _time(lambda: Pr.scale_rows(z, 0.5)), 256 * V * 2 * 2)
     return out
 
 

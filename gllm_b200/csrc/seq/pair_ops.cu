@@ -1,4 +1,4 @@
-// Kernels of the layer-list decoder's hashed pair embedding and scaled logits.
+// Kernel of the layer-list decoder's hashed pair embedding.
 //
 // pair_embed: the fp32 residual stream starts as table[token] + pair_table[row], where row hashes the (previous token,
 // token) pair of the same sequence: (prev * mul_prev + token * mul_cur) mod buckets in 64-bit integers, and a token
@@ -55,14 +55,6 @@ __global__ void __launch_bounds__(128) pair_embed_kernel(const int* __restrict__
   for (int i = threadIdx.x; i < width; i += 128) out[(size_t)t * width + i] = to_f(er[i]) + to_f(pr[i]);
 }
 
-template <typename T>
-__global__ void scale_rows_kernel(T* __restrict__ z, long ld, int n, float scale, size_t total) {
-  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= total) return;
-  const size_t t = i / n, c = i - t * n;
-  z[t * ld + c] = from_f<T>(to_f(z[t * ld + c]) * scale);
-}
-
 }  // namespace
 
 typedef __nv_bfloat16 bf16_t;
@@ -84,17 +76,6 @@ GLLM_EXPORT int gllm_pair_embed(const void* ids, const void* table, const void* 
                                                     (float*)out, width, vocab, mul_prev, mul_cur, buckets,
                                                     (const int*)positions, (int*)prev_state, (const int*)rec_slots,
                                                     (const int*)qsl, nseq);
-  CUDA_CHECK_RET(cudaGetLastError());
-  return 0;
-}
-
-GLLM_EXPORT int gllm_pair_scale_rows(void* z, long ld, int ntok, int n, float scale, int is_f32, void* stream) {
-  if (ntok <= 0 || n <= 0) return 0;
-  cudaStream_t st = (cudaStream_t)stream;
-  const size_t total = (size_t)ntok * n;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
-  if (is_f32) scale_rows_kernel<float><<<blocks, 256, 0, st>>>((float*)z, ld, n, scale, total);
-  else scale_rows_kernel<bf16_t><<<blocks, 256, 0, st>>>((bf16_t*)z, ld, n, scale, total);
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }

@@ -32,14 +32,15 @@ __global__ void embed_scale_kernel(const int* __restrict__ ids, const T* __restr
 
 // x += rms(y) * w_post * post_scale ; x += add ; out = rms(x) * w_pre   (each part optional; post_scale: an fp32
 // layer scale). With emit_plain and no w_pre, out = x rounded to T (sublayers that read the stream un-normed).
-// w_off is added to both norm weights in fp32 (1 for weights stored around zero).
+// w_off is added to both norm weights in fp32 (1 for weights stored around zero); out_mul multiplies the normed
+// output (a logit scale applied to the final norm's result, before it is rounded).
 template <typename T>
 __global__ void __launch_bounds__(256) resid_norm_kernel(float* __restrict__ x, const T* __restrict__ y, long ldy,
                                                          const T* __restrict__ w_post,
                                                          const float* __restrict__ post_scale,
                                                          const float* __restrict__ add, const T* __restrict__ w_pre,
                                                          T* __restrict__ out, int width, float eps, int emit_plain,
-                                                         float w_off) {
+                                                         float w_off, float out_mul) {
   __shared__ float scratch[8];
   const int t = blockIdx.x;
   float* xr = x + (size_t)t * width;
@@ -68,7 +69,8 @@ __global__ void __launch_bounds__(256) resid_norm_kernel(float* __restrict__ x, 
   if (w_pre == nullptr) return;
   ss2 = block_sum<256>(ss2, scratch);
   const float r = 1.0f / sqrtf(ss2 / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += 256) out[(size_t)t * width + i] = from_f<T>(xr[i] * r * (to_f(w_pre[i]) + w_off));
+  for (int i = threadIdx.x; i < width; i += 256)
+    out[(size_t)t * width + i] = from_f<T>(xr[i] * r * (to_f(w_pre[i]) + w_off) * out_mul);
 }
 
 
@@ -416,18 +418,18 @@ GLLM_EXPORT int gllm_seq_embed_scale(const void* ids, const void* table, void* o
 
 GLLM_EXPORT int gllm_seq_resid_norm(void* x, const void* y, long ldy, const void* w_post, const void* post_scale,
                                     const void* add, const void* w_pre, void* out, int ntok, int width, float eps,
-                                    int emit_plain, int is_f32, float w_off, void* stream) {
+                                    int emit_plain, int is_f32, float w_off, float out_mul, void* stream) {
   if (ntok <= 0) return 0;
   cudaStream_t st = (cudaStream_t)stream;
   GLLM_BY_DTYPE(is_f32,
                 (resid_norm_kernel<__nv_bfloat16><<<ntok, 256, 0, st>>>(
                     (float*)x, (const __nv_bfloat16*)y, ldy, (const __nv_bfloat16*)w_post, (const float*)post_scale,
                     (const float*)add, (const __nv_bfloat16*)w_pre, (__nv_bfloat16*)out, width, eps, emit_plain,
-                    w_off)),
+                    w_off, out_mul)),
                 (resid_norm_kernel<float><<<ntok, 256, 0, st>>>((float*)x, (const float*)y, ldy, (const float*)w_post,
                                                                 (const float*)post_scale, (const float*)add,
                                                                 (const float*)w_pre, (float*)out, width, eps,
-                                                                emit_plain, w_off)));
+                                                                emit_plain, w_off, out_mul)));
   CUDA_CHECK_RET(cudaGetLastError());
   return 0;
 }

@@ -126,10 +126,10 @@ def embedding_scaled(ids, table, scale):
     return ref.embedding_scaled(ids, table, scale)
 
 
-def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None, w_offset=0.0):
-    if x.is_cuda:
-        return _seq().resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale, w_offset)
-    return ref.resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale, w_offset)
+def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None, w_offset=0.0,
+               out_mul=1.0):
+    fn = _seq().resid_norm if x.is_cuda else ref.resid_norm
+    return fn(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain, post_scale, w_offset, out_mul)
 
 
 def qk_norm_kv_write(qk, num_heads, num_kv_heads, dim, q_norm_w, k_norm_w, eps, k_cache, v_cache, slots):
@@ -312,8 +312,7 @@ def routed_glu_experts(h, w13, w2, weights, ids, limit, interleaved, alpha=1.702
     return ref.routed_glu_experts(h, w13, w2, weights, ids, limit, alpha)
 
 
-# -- hashed pair embedding with a carried previous token, ungated squared-ReLU experts, scaled logits
-# (csrc/seq/pair_ops.cu) ---------------------------------------------------------------------------------------
+# -- hashed pair embedding with a carried previous token (csrc/seq/pair_ops.cu), ungated squared-ReLU experts ----
 def _pair():
     from gllm_b200.ops import sm100_pair
     return sm100_pair
@@ -334,9 +333,3 @@ def routed_relu2_experts(h, w1, w2, weights, ids, grouped):
     if h.is_cuda:
         return _pair().routed_relu2_experts(h, w1, w2, weights, ids, grouped)
     return ref.routed_relu2_experts(h, w1, w2, weights, ids)
-
-
-def scale_rows(z, scale):
-    if z.is_cuda:
-        return _pair().scale_rows(z, scale)
-    return ref.scale_rows(z, scale)

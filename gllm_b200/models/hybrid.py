@@ -9,7 +9,7 @@ with identity experts and a shared expert); and sandwich blocks whose norm weigh
 `Notadra`: rotary attention with biased projections, YaRN-scaled partial rotation, capped scores, a unit sink in the
 softmax denominator, values of their own width and layers that read an earlier layer's keys and values; a
 sigmoid-scored, group-limited mixture of ungated squared-ReLU experts; a hashed embedding of the (previous, current)
-token pair added to the token embedding; scaled logits):
+token pair added to the token embedding; logits scaled through the final norm):
 
     x = embed[token]
     per layer:  x += ls1 * rms(mixer(x)) * n1 ;  x += ls2 * rms(ff(x)) * n2            (sublayers read x itself)
@@ -43,7 +43,7 @@ Notadra (the sandwich form with gains 1 + w):
 
     x = embed[token] + pair[(previous token * mul_prev + token * mul_cur) mod buckets]   (row `buckets` at position 0)
     per layer:  x += rms(mixer(rms(x) (1 + n1))) (1 + n1b) ;  x += rms(ff(rms(x) (1 + n2))) (1 + n2b)
-    logits = logit_scale * head @ (rms(x) (1 + final_norm))
+    logits = head @ (logit_scale * rms(x) (1 + final_norm))
 
 config.json keys read here: architecture, vocab, width, embedding.scale, embedding.bigram.{buckets, mul_prev,
 mul_cur}, logit_scale, layers[i].mixer.{kv_from, softcap, rot.scaling.{factor, original, fast, slow}},
@@ -308,6 +308,8 @@ class HybridLM(nn.Module):
     def __init__(self, spec: HybridSpec, device="cpu"):
         super().__init__()
         assert ps.get_world_size() == 1, "layer-list decoders run on one GPU (no TP / PP sharding yet)"
+        assert spec.logit_scale == 1.0 or spec.block == "sandwich", \
+            "the logit scale rides on the sandwich form's final norm"
         self.spec = spec
         self.device = torch.device(device)
         h, dt = spec.hidden_size, spec.dtype
@@ -369,8 +371,9 @@ class HybridLM(nn.Module):
             x0 = Fn.embedding_scaled(inp.tokens, self.embed_w, spec.embed_scale)
         x = x0.clone() if any(a for _, a in self.runs) else x0
         n = len(self.runs)
+        # the logit scale rides on the final norm (applied in fp32 before the head's input is rounded)
         h = Fn.resid_norm(x, None, None, None, self.layers[self.runs[0][0]].norm1_w if n else self.final_norm_w,
-                          eps, dt, False, None, off)
+                          eps, dt, False, None, off, 1.0 if n else spec.logit_scale)
         for r, (li, _) in enumerate(self.runs):
             L = self.layers[li]
             y = L.mixer(inp, h, cache, r)
@@ -382,12 +385,13 @@ class HybridLM(nn.Module):
             last = r + 1 == n
             w_pre = self.final_norm_w if last else self.layers[self.runs[r + 1][0]].norm1_w
             add = x0 if (not last and self.runs[r + 1][1]) else None
+            mul = spec.logit_scale if last else 1.0
             if self.trace is not None:
                 Fn.resid_norm(x, y, post, None, None, eps, dt, False, None, off)
                 self.trace.append(x.clone())
-                h = Fn.resid_norm(x, None, None, add, w_pre, eps, dt, False, None, off)
+                h = Fn.resid_norm(x, None, None, add, w_pre, eps, dt, False, None, off, mul)
             else:
-                h = Fn.resid_norm(x, y, post, add, w_pre, eps, dt, False, None, off)
+                h = Fn.resid_norm(x, y, post, add, w_pre, eps, dt, False, None, off, mul)
         return h, None
 
     def _forward_postnorm(self, inp, cache):
@@ -432,8 +436,6 @@ class HybridLM(nn.Module):
     def compute_logits(self, inp, hidden, tpc=None, all_rows: bool = False, local: bool = False):
         rows = hidden if all_rows else hidden.index_select(0, inp.logits_idx.long())
         z = Fn.linear_any(rows, self.lm_head_w)
-        if self.spec.logit_scale != 1.0:
-            z = Fn.scale_rows(z, self.spec.logit_scale)
         return Fn.softcap(z, self.spec.logit_softcap) if self.spec.logit_softcap > 0 else z
 
     # -- weights ----------------------------------------------------------------------------------

@@ -466,12 +466,14 @@ def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> to
 
 def resid_norm(x: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torch.Tensor],
                add: Optional[torch.Tensor], w_pre: Optional[torch.Tensor], eps: float, out_dtype,
-               emit_plain: bool = False, post_scale: Optional[torch.Tensor] = None, w_offset: float = 0.0):
+               emit_plain: bool = False, post_scale: Optional[torch.Tensor] = None, w_offset: float = 0.0,
+               out_mul: float = 1.0):
     """In place on the fp32 stream x [T, W]:  x += rms(y) * w_post ;  x += add ;  returns rms(x) * w_pre cast to
     `out_dtype` (None when w_pre is None). Every step is optional. All arithmetic in fp32. `post_scale` [W] fp32
     (a layer scale) multiplies the normed branch element by element: x += rms(y) * w_post * post_scale. `emit_plain` (with w_pre None): returns the stream itself rounded to
     `out_dtype` — x for fp32 — for sublayers that read the stream without a norm in front. `w_offset` is added to
-    both norm weights in fp32 (1.0 for weights stored around zero)."""
+    both norm weights in fp32 (1.0 for weights stored around zero); `out_mul` multiplies the normed result before it
+    is rounded (a logit scale folded into the final norm)."""
     if y is not None:
         yf = y.float()
         br = yf * torch.rsqrt((yf * yf).mean(-1, keepdim=True) + eps) * (w_post.float() + w_offset)
@@ -482,7 +484,7 @@ def resid_norm(x: torch.Tensor, y: Optional[torch.Tensor], w_post: Optional[torc
         if emit_plain:
             return x if out_dtype == torch.float32 else x.to(out_dtype)
         return None
-    return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * (w_pre.float() + w_offset)).to(out_dtype)
+    return (x * torch.rsqrt((x * x).mean(-1, keepdim=True) + eps) * (w_pre.float() + w_offset) * out_mul).to(out_dtype)
 
 
 def _cache_rows_write(cache: torch.Tensor, slots: torch.Tensor, rows: torch.Tensor):
@@ -992,7 +994,7 @@ def routed_glu_experts(h: torch.Tensor, w13: torch.Tensor, w2: torch.Tensor, wei
 
 
 # ----------------------------------------------------------------------------------------------
-# hashed pair embedding with a carried previous token, ungated squared-ReLU experts, scaled logits
+# hashed pair embedding with a carried previous token, ungated squared-ReLU experts
 # (PyTorch forms of the kernels in csrc/seq/pair_ops.cu)
 # ----------------------------------------------------------------------------------------------
 def embedding_pair_hash(ids: torch.Tensor, table: torch.Tensor, pair_table: torch.Tensor, mul_prev: int, mul_cur: int,
@@ -1033,7 +1035,3 @@ def routed_relu2_experts(h: torch.Tensor, w1: torch.Tensor, w2: torch.Tensor, we
             a = relu2(linear(h[rows], w1[e]))
             out[rows] += weights[rows, kk].float().unsqueeze(1) * linear(a, w2[e]).float()
     return out.to(h.dtype)
-
-
-def scale_rows(z: torch.Tensor, scale: float) -> torch.Tensor:
-    return (z.float() * scale).to(z.dtype)

@@ -1,6 +1,6 @@
 """Python front-ends of csrc/seq/pair_ops.cu and of the ungated squared-ReLU expert path (ctypes ->
 libgllm_b200.so): hashed pair embedding with a carried previous token, routed experts down(relu(up h)^2) on the
-grouped tcgen05 GEMM pair or the plain per-slot kernels, scaled logits. No fallback: a missing library on a GPU box
+grouped tcgen05 GEMM pair or the plain per-slot kernels. No fallback: a missing library on a GPU box
 raises."""
 from __future__ import annotations
 
@@ -25,7 +25,6 @@ def _L():
         P, I, G, F = c_void_p, c_int, c_long, c_float
         sigs = {
             "gllm_pair_embed": [P, P, P, P, I, I, I, G, G, I, P, P, P, P, I, I, P],
-            "gllm_pair_scale_rows": [P, G, I, I, F, I, P],
             "gllm_moe_grouped_gemm_act": [P, ctypes.c_int64, P, P, ctypes.c_int64, I, I, I, I, P, P, I, P],
         }
         for name, args in sigs.items():
@@ -57,14 +56,6 @@ def embedding_pair_hash(ids, table, pair_table, mul_prev, mul_cur, buckets, posi
           "pair_embed")
     sm100._count()
     return out
-
-
-def scale_rows(z, scale):
-    assert z.stride(1) == 1
-    check(_L().gllm_pair_scale_rows(_p(z), z.stride(0), z.shape[0], z.shape[1], float(scale), _f32(z), stream_ptr()),
-          "pair_scale_rows")
-    sm100._count()
-    return z
 
 
 def routed_relu2_experts(h, w1, w2, weights, ids, grouped: bool):

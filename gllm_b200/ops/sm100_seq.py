@@ -26,7 +26,7 @@ def _L():
         P, I, G, F = c_void_p, c_int, c_long, c_float
         sigs = {
             "gllm_seq_embed_scale": [P, P, P, I, I, I, F, I, P],
-            "gllm_seq_resid_norm": [P, P, G, P, P, P, P, P, I, I, F, I, I, F, P],
+            "gllm_seq_resid_norm": [P, P, G, P, P, P, P, P, I, I, F, I, I, F, F, P],
             "gllm_seq_qk_norm_kv_write": [P, G, I, I, I, I, P, P, F, P, P, P, P, I, I, I, P],
             "gllm_seq_window_attention": [P, P, P, P, I, P, P, I, I, F, I, I, I, I, I, I, P, P, G, F, I, I, I, I, F, P],
             "gllm_seq_postnorm": [P, P, G, P, P, I, I, F, F, I, P],
@@ -101,7 +101,8 @@ def embedding_scaled(ids: torch.Tensor, table: torch.Tensor, scale: float) -> to
     return out
 
 
-def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None, w_offset=0.0):
+def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_scale=None, w_offset=0.0,
+               out_mul=1.0):
     assert x.dtype == torch.float32 and x.is_contiguous()
     t, width = x.shape
     plain = bool(emit_plain) and w_pre is None
@@ -122,7 +123,7 @@ def resid_norm(x, y, w_post, add, w_pre, eps, out_dtype, emit_plain=False, post_
         return x if ret_x else None
     check(_L().gllm_seq_resid_norm(_p(x), _p(y), y.stride(0) if y is not None else 0, _p(w_post), _p(post_scale),
                                    _p(add), _p(w_pre), _p(out), t, width, float(eps), int(plain), is32, float(w_offset),
-                                   stream_ptr()),
+                                   float(out_mul), stream_ptr()),
           "seq_resid_norm")
     sm100._count()
     return x if ret_x else out

@@ -73,8 +73,8 @@ def _batch(qlens, ctx, ps, pages):
 
 # -- kernels against their unfused forms ---------------------------------------------------------------------------
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 3e-5), (torch.bfloat16, 2e-2)])
-def test_stream_norm_offset_bias_and_scaled_rows(dt, tol):
-    from gllm_b200.ops import ref, sm100_pair as P, sm100_seq as K
+def test_stream_norm_offset_scale_and_bias(dt, tol):
+    from gllm_b200.ops import ref, sm100_seq as K
     torch.manual_seed(1)
     for T, width in ((1, 8), (37, 100), (300, 1024)):
         x = torch.randn(T, width, device=DEV) * 3
@@ -91,8 +91,10 @@ def test_stream_norm_offset_bias_and_scaled_rows(dt, tol):
         want = (a.float() @ w.float().t() + b.float())
         assert close(K.linear_any(a, w, b), want, tol), (m, k, n)
         assert close(K.gemm_simt(a, w, b), want, tol), (m, k, n)
-    z = torch.randn(9, 50, device=DEV).to(dt)
-    assert close(P.scale_rows(z.clone(), 0.37), ref.scale_rows(z, 0.37), 1e-6 if dt == torch.float32 else 4e-3)
+    x = torch.randn(9, 50, device=DEV)
+    wq = (torch.randn(50, device=DEV) * 0.3).to(dt)
+    o1 = K.resid_norm(x.clone(), None, None, None, wq, 1e-5, dt, False, None, 1.0, 0.37)          # scaled final norm
+    assert close(o1, ref.resid_norm(x.clone(), None, None, None, wq, 1e-5, dt, False, None, 1.0, 0.37), tol)
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
